@@ -114,7 +114,17 @@ class CacheManager:
         self.site_cache: list = [None] * len(needs)
         self._slot_sites: list[int] = []
         by_need: dict[PagedNeed, PageGroup] = {}
+        # a site's need may be a tuple of needs (a mixer that keeps pages and a state): its cache is the tuple of theirs
+        flat: list[tuple[int, int | None, object]] = []       # (site, place in the site's tuple or None, need)
         for i, need in enumerate(needs):
+            if isinstance(need, (tuple, list)):
+                flat += [(i, j, n) for j, n in enumerate(need)]
+                self.site_cache[i] = [None] * len(need)
+            else:
+                flat.append((i, None, need))
+        paged: list[tuple[PageGroup, int, int | None]] = []
+        slotted: list[tuple[int, int | None, SlotNeed]] = []
+        for i, j, need in flat:
             if isinstance(need, PagedNeed):
                 if need.window is not None and need.window <= 0:
                     raise ValueError(f"site {i}: window {need.window} must be positive")
@@ -122,29 +132,42 @@ class CacheManager:
                     by_need[need] = PageGroup(need, [], PagePool(num_pages), page_size)
                     self.groups.append(by_need[need])
                 by_need[need].sites.append(i)
+                paged.append((by_need[need], i, j))
             elif isinstance(need, SlotNeed):
                 self._slot_sites.append(i)
+                slotted.append((i, j, need))
             elif need is not None:
                 raise TypeError(f"site {i}: unknown cache need {need!r}")
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._slot_of: dict = {}
         self._length: dict = {}
         self.preemptions = 0
-        self._slot_init: dict[int, object] = {}       # site -> what a slot is set to when a request takes it
+        self._slot_states: list[tuple[torch.Tensor, object]] = []   # (state tensor, what a slot is set to when taken)
+
+        def put(i: int, j: int | None, made) -> None:
+            if j is None:
+                self.site_cache[i] = made
+            else:
+                self.site_cache[i][j] = made
+
         if device is not None:
-            for gi, g in enumerate(self.groups):
+            for g, i, j in paged:
+                gi = self.groups.index(g)
                 shape = (num_pages, g.need.kv_heads, page_size, g.need.head_dim)
-                for i in g.sites:
-                    k = torch.zeros(shape, dtype=dtype, device=device)
-                    v = torch.zeros(shape, dtype=dtype, device=device) if g.need.values else k
-                    self.site_cache[i] = PagedSiteCache(gi, page_size, k, v)
-            for i in self._slot_sites:
-                need = needs[i]
-                self.site_cache[i] = SlotSiteCache(torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=device))
+                k = torch.zeros(shape, dtype=dtype, device=device)
+                if not g.need.values:
+                    v = k
+                else:
+                    v = torch.zeros(shape[:3] + (g.need.value_dim or g.need.head_dim,), dtype=dtype, device=device)
+                put(i, j, PagedSiteCache(gi, page_size, k, v))
+            for i, j, need in slotted:
+                state = torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=device)
+                put(i, j, SlotSiteCache(state))
                 init = need.init
                 if isinstance(init, torch.Tensor):
                     init = init.to(device=device, dtype=need.dtype)
-                self._slot_init[i] = init
+                self._slot_states.append((state, init))
+            self.site_cache = [tuple(c) if isinstance(c, list) else c for c in self.site_cache]
 
     # ---- requests ----
     def admit(self, req) -> int:
@@ -161,14 +184,13 @@ class CacheManager:
             g.tables[req] = []
             g.arrays[req] = np.empty(64, dtype=np.int32)
         if self.device is not None:
-            for i in self._slot_sites:
-                init = self._slot_init.get(i)
+            for state, init in self._slot_states:
                 if init is None:
-                    self.site_cache[i].state[slot].zero_()
+                    state[slot].zero_()
                 elif isinstance(init, torch.Tensor):
-                    self.site_cache[i].state[slot].copy_(init.expand_as(self.site_cache[i].state[slot]))
+                    state[slot].copy_(init.expand_as(state[slot]))
                 else:
-                    self.site_cache[i].state[slot].fill_(init)
+                    state[slot].fill_(init)
         return slot
 
     def has(self, req) -> bool:
@@ -210,13 +232,15 @@ class CacheManager:
                 continue
             # the next row sits at position new_len and reads positions >= new_len - w + 1
             first_needed = max(0, new_len - w + 1) // g.page_size
+            kept = -(-g.need.keep_first // g.page_size)       # pages that hold positions every later row still reads
             table = g.tables[req]
-            gone = [p for p in table[:first_needed] if p >= 0]
+            stop = min(first_needed, len(table))
+            gone = [p for p in table[kept:stop] if p >= 0]
             if gone:
                 g.pool.give_back(gone, req)
-                for j in range(min(first_needed, len(table))):
+                for j in range(kept, stop):
                     table[j] = -1
-                g.arrays[req][:min(first_needed, len(table))] = -1
+                g.arrays[req][kept:stop] = -1
 
     def free(self, req) -> None:
         """The request ends (or is preempted): every page and the slot go back."""

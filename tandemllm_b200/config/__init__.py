@@ -8,6 +8,9 @@ from .registry import (REGISTRY, Architecture, architecture_of, read_model_confi
 from .puripel import ARCHITECTURES as _PURIPEL_ARCHS
 from .puripel import MODEL_TYPES as _PURIPEL_TYPES
 from .puripel import PuripelConfig
+from .sebilorn import ARCHITECTURES as _SEBILORN_ARCHS
+from .sebilorn import MODEL_TYPES as _SEBILORN_TYPES
+from .sebilorn import SebilornConfig
 from .sifupel import ARCHITECTURES as _SIFUPEL_ARCHS
 from .sifupel import MODEL_TYPES as _SIFUPEL_TYPES
 from .sifupel import SifupelConfig
@@ -22,6 +25,9 @@ register(Architecture(name="sifupel", architectures=_SIFUPEL_ARCHS, model_types=
 register(Architecture(name="puripel", architectures=_PURIPEL_ARCHS, model_types=_PURIPEL_TYPES,
                       read_config=PuripelConfig.from_dict))
 
-__all__ = ["PuripelConfig", "REGISTRY", "Architecture", "architecture_of", "read_model_config", "register", "unregister",
+register(Architecture(name="sebilorn", architectures=_SEBILORN_ARCHS, model_types=_SEBILORN_TYPES,
+                      read_config=SebilornConfig.from_dict))
+
+__all__ = ["PuripelConfig", "SebilornConfig", "REGISTRY", "Architecture", "architecture_of", "read_model_config", "register", "unregister",
            "resolve_model_folder", "spec_of", "LayerSpec", "ModelSpec", "PartSpec", "Site", "StreamAdd", "plain_schedule",
            "Lfm2MoeConfig", "SifupelConfig"]

@@ -78,6 +78,8 @@ class ModelSpec:
     embedding_name: str = field(kw_only=True)       # the embedding table's tensor name; an architecture says its own
     final_norm_prefix: str = field(kw_only=True)    # the last norm's part of its tensors' names
     head_name: str | None = None           # None: the head is the embedding (tied)
+    embedding_scale: float = 1.0           # every embedded row is multiplied by this (32-bit)
+    logit_softcap: float | None = None     # c: logits <- c tanh(logits / c); None: the logits stay as the head made them
     ignored_names: tuple[str, ...] = ()    # stored tensors that are neither read nor an error (a tied model's copy
                                            # of its head, for one)
     max_positions: int = 1 << 17

@@ -20,10 +20,10 @@ extern "C" const char* tl_cuda_error_string(int code) { return cudaGetErrorStrin
 
 namespace tl {
 
-// residual[r, :] = float(table[token[r], :])
+// residual[r, :] = float(table[token[r], :]) * scale
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                                  float* __restrict__ residual, int hidden, int vocab, int* __restrict__ status) {
+                                  float* __restrict__ residual, int hidden, int vocab, int* __restrict__ status, float scale) {
   chain_next();
   chain_wait();
   const int r = blockIdx.x;
@@ -34,7 +34,7 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
   }
   const T* src = table + (size_t)tok * hidden;
   float* dst = residual + (size_t)r * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]) * scale;
 }
 
 // What is added to the residual before the norm. The previous branch's output comes in one of three forms, so
@@ -478,17 +478,17 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 using namespace tl;
 
 extern "C" int tl_embed_rows(const void* table, const int* tokens, float* residual, int rows, int hidden, int vocab,
-                             int dtype, int* status, cudaStream_t stream) {
+                             int dtype, int* status, float scale, cudaStream_t stream) {
   if (rows == 0) return 0;
   TL_REQUIRE(rows > 0 && hidden > 0 && vocab > 0, "embed_rows: rows %d hidden %d vocab %d", rows, hidden, vocab);
   const int threads = hidden >= 1024 ? 256 : 128;
   cudaError_t e;
   if (dtype == TL_FP32)
     e = launch_chained(embed_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, (const float*)table, tokens, residual,
-                       hidden, vocab, status);
+                       hidden, vocab, status, scale);
   else
     e = launch_chained(embed_rows_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, (const bf16*)table, tokens, residual,
-                       hidden, vocab, status);
+                       hidden, vocab, status, scale);
   return (int)e;
 }
 

@@ -432,11 +432,12 @@ class Engine:
         """Bytes one decode step of `batch` requests at `context` tokens has to read: see `DecoderModel.decode_bytes`,
         plus the keys and values of the live requests in every page group (a windowed group holds its window)."""
         out = self.model.decode_bytes(batch, experts_read)
-        elem = self.cache.site_cache[self.cache.groups[0].sites[0]].k.element_size() if self.cache.groups else 0
+        elem = torch.empty(0, dtype=self.cache.dtype).element_size() if self.cache.groups else 0
         kv = 0
         for g in self.cache.groups:
-            span = context if g.need.window is None else min(context, g.need.window)
-            kv += len(g.sites) * 2 * g.need.kv_heads * g.need.head_dim * elem * span * batch
+            span = context if g.need.window is None else min(context, g.need.window + g.need.keep_first)
+            per_token = g.need.head_dim + ((g.need.value_dim or g.need.head_dim) if g.need.values else 0)
+            kv += len(g.sites) * g.need.kv_heads * per_token * elem * span * batch
         out["kv"] = kv
         out["total"] += kv
         return out

@@ -117,7 +117,7 @@ class Scheduler:
         most = min(n + request.params.max_tokens, self.max_model_len)
         ps = self.cache.page_size
         for g in self.cache.groups:
-            span = most if g.need.window is None else min(most, g.need.window + self.chunk_size + ps)
+            span = most if g.need.window is None else min(most, g.need.window + self.chunk_size + ps + g.need.keep_first)
             if -(-span // ps) > g.pool.num_pages:
                 raise ValueError(f"request {request.request_id!r}: {most} tokens need {-(-span // ps)} pages, "
                                  f"the pool has {g.pool.num_pages}")
@@ -136,7 +136,7 @@ class Scheduler:
 
     def _whole_text_fits(self, newcomer: Request, chosen: list[tuple[Request, int]]) -> bool:
         """Whether the free pages cover what the running requests and `newcomer` need to feed all the text they have
-        (a group with a window never holds more than its window, a portion and a page of one request)."""
+        (a group with a window never holds more than its window, the first tokens it keeps, a portion and a page of one request)."""
         ps = self.cache.page_size
         totals = {id(q): (q, len(q.prompt) + len(q.output)) for q in self.running}
         totals[id(newcomer)] = (newcomer, len(newcomer.prompt) + len(newcomer.output))
@@ -146,7 +146,7 @@ class Scheduler:
                 table = g.tables.get(q.request_id, [])
                 more = -(-total // ps) - len(table)
                 if g.need.window is not None:
-                    span = -(-(g.need.window + self.chunk_size + ps) // ps)
+                    span = -(-(g.need.window + self.chunk_size + ps + g.need.keep_first) // ps)
                     more = min(more, span - sum(1 for p in table if p >= 0))
                 need += max(0, more)
             if need > g.pool.free:

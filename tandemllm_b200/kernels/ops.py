@@ -18,7 +18,7 @@ FP32, BF16 = 0, 1
 TL_BAD_ARGUMENT = 100001
 # the gate activations of gated products (TL_ACT_* of csrc/common.cuh) and the router's scoring functions (TL_SCORE_*
 # of csrc/route.cuh), by the names a part's spec gives them
-ACTIVATIONS = {"silu": 1, "gelu": 2, "relu2": 3, "identity": 4, "xielu": 5, "clamped_swish": 6}
+ACTIVATIONS = {"silu": 1, "gelu": 2, "relu2": 3, "identity": 4, "xielu": 5, "clamped_swish": 6, "softcap": 7, "tanh": 8}
 SCORINGS = {"sigmoid": 0, "softmax": 1}
 
 
@@ -62,7 +62,7 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 
 _SIGNATURES = {
-    "tl_embed_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "tl_embed_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p],
     "tl_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                        c_void_p,
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -123,6 +123,19 @@ _SIGNATURES = {
                        c_int, c_int, c_void_p],
     "tl_attention_latent": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "tl_add_layernorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                         c_int, c_void_p],
+    "tl_qkv_rotate_store": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p, c_void_p],
+    "tl_attention_flex": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float,
+                          c_int, c_int, c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_longlong, c_int, c_int, c_int,
+                          c_int, c_int, c_int, c_void_p, c_void_p],
+    "tl_recurrence_scan": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                           c_float, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                           c_int, c_int, c_void_p],
+    "tl_group_norm_gate": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_float, c_float, c_void_p, c_longlong, c_int,
+                           c_int, c_int, c_int, c_void_p],
     "tl_set_gate_constants": [c_float, c_float],
     "tl_graph_capture_begin": [c_void_p],
     "tl_graph_capture_end": [c_void_p, c_void_p, c_void_p],
@@ -198,11 +211,13 @@ def _need(t: torch.Tensor, dtype: torch.dtype | None, name: str) -> None:
 
 
 # ------------------------------------------------------------------------------------------ rows
-def embed_rows(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor, status: torch.Tensor) -> None:
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor, status: torch.Tensor,
+               scale: float = 1.0) -> None:
+    """residual[r] = table[tokens[r]] * scale in 32-bit."""
     _need(table, None, "embedding table"); _need(tokens, torch.int32, "tokens"); _need(residual, torch.float32, "residual")
     rows, hidden = residual.shape
     check(core().tl_embed_rows(ptr(table), ptr(tokens), ptr(residual), rows, hidden, table.shape[0],
-                               dtype_code(table.dtype), ptr(status), stream()), "embed_rows")
+                               dtype_code(table.dtype), ptr(status), float(scale), stream()), "embed_rows")
 
 
 class PartialSums:
@@ -336,6 +351,30 @@ def activation(x: torch.Tensor, out: torch.Tensor, act: int, a0: float = 0.0, a1
     _need(x, out.dtype, "x"); _need(out, None, "out")
     check(core().tl_activation(ptr(x), ptr(out), x.numel(), int(act), float(a0), float(a1), dtype_code(out.dtype), stream()),
           "activation")
+    return out
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap), in place."""
+    return activation(x, x, ACTIVATIONS["softcap"], float(cap))
+
+
+def add_layernorm(residual: torch.Tensor, delta, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
+                  gather: torch.Tensor | None = None) -> torch.Tensor:
+    """residual += delta (None, a float32 tensor or `PartialSums`); out = (residual - mean) / sqrt(var + eps) * weight + bias,
+    mean and variance over the row in 32-bit. With `gather` output row i is made from row gather[i] and the residual stays."""
+    _need(residual, torch.float32, "residual"); _need(out, None, "out")
+    parts, stride, data = 0, 0, None
+    if isinstance(delta, PartialSums):
+        parts, data = delta.parts, delta.data
+        stride = delta.rows * delta.hidden
+    elif delta is not None:
+        delta = materialize(delta)
+        _need(delta, torch.float32, "delta")
+        parts, data = 1, delta
+    check(core().tl_add_layernorm(ptr(residual), ptr(data), parts, stride, ptr(weight), ptr(bias), float(eps), ptr(out),
+                                  ptr(gather), out.shape[0], residual.shape[-1], dtype_code(out.dtype), stream()),
+          "add_layernorm")
     return out
 
 
@@ -647,6 +686,71 @@ def attention_join(scratch, positions, window, out, n_spans: int, span_keys: int
     check(core().tl_attention_join(ptr(scratch), ptr(positions), int(window or 0), ptr(out), rows, Hq, D, int(n_spans),
                                    int(span_keys), dtype_code(out.dtype), stream()), "attention_join",
           kernels=1 if n_spans > 1 else 0)
+
+
+def qkv_rotate_store(qkv, q_col: int, k_col: int, v_col: int, inv_freq, rot: int, inv_freq_v, positions, req_of_row, table,
+                     page_size: int, q_out, k_cache, v_cache, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                     status) -> None:
+    """From the rows of one fused product (`q_col`, `k_col`, `v_col`: where each part begins in a row; `k_col` < 0: the rows
+    hold queries only): rotary over the first `rot` entries of every q and k head (halves layout; `inv_freq` None: none), the
+    values turned over all their entries by `inv_freq_v` (None: as projected); q to `q_out`, k and v into their pages."""
+    _need(qkv, None, "qkv"); _need(q_out, qkv.dtype, "q")
+    check(core().tl_qkv_rotate_store(ptr(qkv), qkv.stride(0), int(q_col), int(k_col), int(v_col), ptr(inv_freq), int(rot),
+                                     ptr(inv_freq_v), ptr(positions), ptr(req_of_row), ptr(table),
+                                     table.shape[1] if table is not None else 0, int(page_size),
+                                     k_cache.shape[0] if k_cache is not None else 0, ptr(q_out), ptr(k_cache), ptr(v_cache),
+                                     qkv.shape[0], num_heads, num_kv_heads, head_dim, value_dim, dtype_code(qkv.dtype),
+                                     ptr(status), stream()), "qkv_rotate_store")
+
+
+def attention_flex(q, k_cache, v_cache, table, page_size: int, req_of_row, positions, scale: float, softcap, window,
+                   keep_first: int, inv_freq_out, gate, ld_gate: int, out_scale: float, out, status) -> torch.Tensor:
+    """Attention of every row over its request's pages: capped scores (`softcap` None: none), a window that also keeps the
+    first `keep_first` tokens (`window` None: all keys), the output turned back by `inv_freq_out` (None: not), times
+    sigmoid(`gate`) entry by entry (a tensor of the compute dtype beginning at the first logit, rows `ld_gate` apart), times
+    `out_scale`. `out` [rows, heads * value_dim] may be a column slice of a wider tensor."""
+    _need(q, k_cache.dtype, "q")
+    rows, Hq, D = q.shape
+    Hk, VD = k_cache.shape[1], v_cache.shape[3]
+    if out.dtype != q.dtype or out.stride(1) != 1 or out.shape != (rows, Hq * VD):
+        raise KernelError(f"attention output of shape {tuple(out.shape)}, dtype {out.dtype}")
+    check(core().tl_attention_flex(ptr(q), ptr(k_cache), ptr(v_cache), ptr(table), table.shape[1], int(page_size),
+                                   k_cache.shape[0], ptr(req_of_row), ptr(positions), float(scale), float(softcap or 0.0),
+                                   int(window or 0), int(keep_first or 0), ptr(inv_freq_out), ptr(gate), int(ld_gate),
+                                   float(out_scale), ptr(out), out.stride(0), rows, Hq, Hk, D, VD, dtype_code(q.dtype),
+                                   ptr(status), stream()), "attention_flex")
+    return out
+
+
+def recurrence_scan(proj, q_col: int, k_col: int, v_col: int, state, state_slot, row_start, requests: int, y, heads: int,
+                    key_dim: int, value_dim: int, *, head_decay=None, a_col: int = -1, w=None, w0=None, a_bias=None,
+                    rate: float = 0.0, key_eps: float = 0.0, silu_inputs: bool = False, write_state: bool = True) -> torch.Tensor:
+    """The recurrence over a matrix state a head (csrc/recurrence.cu): with `head_decay` (float32 [heads]) the decayed sum of
+    outer products, with `w` (float32 [rows, heads * key_dim], the decay's logits) the generalized delta rule. `proj`:
+    float32 rows holding q, k, v (and the removal logits at `a_col`) at the given columns; `state` [slots, heads, key_dim,
+    value_dim] float32; `y` [rows, heads * value_dim] float32."""
+    _need(proj, torch.float32, "projections"); _need(state, torch.float32, "state"); _need(y, torch.float32, "y")
+    if w is not None:
+        _need(w, torch.float32, "decay logits")
+    check(core().tl_recurrence_scan(ptr(proj), proj.stride(0), int(q_col), int(k_col), int(v_col), int(a_col), ptr(w),
+                                    w.stride(0) if w is not None else 0, ptr(w0), ptr(a_bias), ptr(head_decay), float(rate),
+                                    float(key_eps), int(silu_inputs), ptr(state), state[0].numel(), ptr(state_slot),
+                                    ptr(row_start), int(requests), ptr(y), heads, key_dim, value_dim, int(write_state),
+                                    stream()), "recurrence_scan")
+    return y
+
+
+def group_norm_gate(y, gate, ld_gate: int, weight, eps: float, groups: int, scale: float, out) -> torch.Tensor:
+    """out = y / rms(y) over each of `groups` equal parts of a row, times `weight`, times sigmoid(gate), times `scale`. `gate`
+    begins at the first logit, rows `ld_gate` apart (32-bit or the compute dtype); `out` may be a column slice."""
+    _need(y, torch.float32, "y")
+    rows, width = y.shape
+    if out.stride(1) != 1 or out.shape != (rows, width):
+        raise KernelError(f"group_norm_gate output of shape {tuple(out.shape)}")
+    check(core().tl_group_norm_gate(ptr(y), ptr(gate), int(ld_gate), dtype_code(gate.dtype), ptr(weight), float(eps),
+                                    float(scale), ptr(out), out.stride(0), rows, width, int(groups), dtype_code(out.dtype),
+                                    stream()), "group_norm_gate")
+    return out
 
 
 HEADMIX_SPAN = 32       # the fewest keys a span of `attention_headmix` holds: one tile (measured: 40 us a layer at 8 rows and a window of 1024 against 49 with 64 and 82 with 128)

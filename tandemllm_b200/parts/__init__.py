@@ -1,6 +1,6 @@
 """Layers put together from parts: mixers, feed-forwards, norms, position encodings, arrangements."""
 
-from . import attention, block, feed_forward, latent_attention, norm, position, short_conv, state_space  # noqa: F401  (each registers its kinds)
+from . import attention, block, feed_forward, latent_attention, linear_recurrence, norm, position, short_conv, state_space  # noqa: F401  (each registers its kinds)
 from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, PagedNeed, PagedSiteCache, Part,
                    Runtime, SlotNeed, SlotSiteCache, StepContext, make_part, register_part)
 from .block import Layer

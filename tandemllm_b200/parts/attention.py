@@ -11,7 +11,16 @@ Options, each a parameter of the spec so that another design can name its own co
   `head_mix`: the name of a tensor M [Hq, Hq]: after the softmax the heads' weights are mixed, p'_h = sum_g M[h, g] p_g,
               and head h applies p'_h to the values of its own KV head;
   `gate`: the name of a matrix [Hq, hidden]: head h's output is multiplied by sigmoid(gate n)_h before the out projection;
-  `weight_suffix`: what follows a matrix's name in the folder (".weight" by default).
+  `weight_suffix`: what follows a matrix's name in the folder (".weight" by default);
+  `value_dim`: the size of a value a head where it is not the keys';
+  `softcap` c: score <- c tanh(score / c) before the mask and the softmax;
+  `keep_first` n (with a window): a row also sees the keys at positions below n, at their true positions;
+  `value_rotation` base: the value at position j is turned by j over all its entries (halves layout, pair m by
+              j base^(-2m / value_dim)) and cached so; a head's output at position i is turned back by -i before any gate;
+  `entry_gate`: the name of a matrix [Hq * value_dim, hidden]: the concatenated heads times sigmoid(gate n) entry by entry;
+  `borrows_keys`: the layer has no k and v matrices: its site reads the cache of the site its run order names;
+  `cache_window`, `cache_keep_first`: what the pages must keep readable when other sites read them through wider masks.
+Any of these takes the mixer to the kernels of csrc/attention_flex.cu, which have all of them as arguments.
 
 Every size (heads, KV heads, head size), the scale, the window and the names of its tensors are
 parameters. The q, k and v matrices are fused into one product at bind time, as the reference's loader
@@ -44,6 +53,10 @@ class AttentionMixer(Part):
         if spec.get("head_mix") or spec.get("gate"):
             if not 1 <= self.head_dim <= 256:       # the head-mixing kernels take any head size the q/k kernel does
                 raise ValueError(f"head size {self.head_dim}: 1 to 256 are implemented")
+        elif any(spec.get(k) for k in ("softcap", "keep_first", "value_rotation", "entry_gate", "borrows_keys")) or \
+                int(spec.get("value_dim") or self.head_dim) != self.head_dim:
+            if not (1 <= self.head_dim <= 256 and 1 <= int(spec.get("value_dim") or self.head_dim) <= 256):
+                raise ValueError(f"head sizes {self.head_dim} and {spec.get('value_dim')}: 1 to 256 are implemented")
         elif self.head_dim % 16 or not 16 <= self.head_dim <= 256:
             raise ValueError(f"head size {self.head_dim}: multiples of 16 from 16 to 256 are implemented")
         self.scale = float(spec.get("scale") or self.head_dim ** -0.5)
@@ -64,6 +77,27 @@ class AttentionMixer(Part):
         self.qk_flags = (ops.QK_UNIT_NORM if qk and qk.kind == "unit_rms" else 0) | \
                         (ops.QK_VALUES_ARE_KEYS if self.values == "keys" else 0)
         self.head_mix = None
+        self.value_dim = int(spec.get("value_dim") or self.head_dim)
+        self.softcap = spec.get("softcap")
+        self.keep_first = int(spec.get("keep_first") or 0)
+        self.value_rotation = spec.get("value_rotation")
+        self.entry_gate_name = prefix + spec["entry_gate"] if spec.get("entry_gate") else None
+        self.borrows_keys = bool(spec.get("borrows_keys", False))
+        self.cache_window = spec.get("cache_window", self.window)
+        self.cache_keep_first = int(spec.get("cache_keep_first", self.keep_first) or 0)
+        self.flex = bool(self.value_dim != self.head_dim or self.softcap or self.keep_first or self.value_rotation
+                         or self.entry_gate_name or self.borrows_keys)
+        if self.flex:
+            if self.head_mix_name or self.gate_name or self.q_norm or self.values != "projected" or self.bias:
+                raise ValueError("capped scores, kept first tokens, turned values, an entry-wise gate and borrowed keys do "
+                                 "not combine with mixed heads, a gate a head, q/k norms or values that are the keys")
+            if self.value_rotation and self.value_dim % 2:
+                raise ValueError(f"values of odd size {self.value_dim} cannot be turned in pairs")
+        self.inv_freq_v = None
+
+    @property
+    def out_dim(self) -> int:
+        return self.num_heads * self.value_dim
 
     @property
     def q_dim(self) -> int:
@@ -75,6 +109,14 @@ class AttentionMixer(Part):
 
     def weight_specs(self, present=None):
         H, sfx = self.hidden_size, self.suffix
+        if self.flex:
+            out = [TensorSpec(self.n["q"] + sfx, (self.q_dim, H))]
+            if not self.borrows_keys:
+                out += [TensorSpec(self.n["k"] + sfx, (self.kv_dim, H)),
+                        TensorSpec(self.n["v"] + sfx, (self.num_kv_heads * self.value_dim, H))]
+            if self.entry_gate_name:
+                out.append(TensorSpec(self.entry_gate_name + sfx, (self.out_dim, H)))
+            return out + [TensorSpec(self.n["out"] + sfx, (H, self.out_dim))]
         out = [TensorSpec(self.n["q"] + sfx, (self.q_dim, H)), TensorSpec(self.n["k"] + sfx, (self.kv_dim, H))]
         if self.values == "projected":
             out.append(TensorSpec(self.n["v"] + sfx, (self.kv_dim, H)))
@@ -90,6 +132,27 @@ class AttentionMixer(Part):
     def bind(self, read, runtime):
         self.runtime = runtime
         sfx = self.suffix
+        if self.flex:
+            # one product for everything that reads the normed row: q, then k and v (unless borrowed), then the gate; every
+            # part begins at a multiple of 8 columns
+            parts = ["q"] + ([] if self.borrows_keys else ["k", "v"])
+            mats = [(x, runtime.matrix(read(self.n[x] + sfx))) for x in parts]
+            if self.entry_gate_name:
+                mats.append(("gate", runtime.matrix(read(self.entry_gate_name + sfx))))
+            rows, self.col, at = [], {}, 0
+            for name, m in mats:
+                self.col[name] = at
+                pad = -m.shape[0] % 8
+                rows += [m, torch.zeros(pad, m.shape[1], dtype=m.dtype, device=m.device)] if pad else [m]
+                at += m.shape[0] + pad
+            self.w_qkv = torch.cat(rows).contiguous()
+            self.w_out = runtime.matrix(read(self.n["out"] + sfx))
+            self.position.bind(read, runtime)
+            if self.value_rotation:
+                vd = self.value_dim
+                f = float(self.value_rotation) ** (-torch.arange(0, vd, 2, dtype=torch.float64) / vd)
+                self.inv_freq_v = f.to(torch.float32).to(runtime.device)
+            return
         rows = [runtime.matrix(read(self.n[x] + sfx)) for x in (("q", "k", "v") if self.values == "projected" else ("q", "k"))]
         self.gate_at = sum(r.shape[0] for r in rows)        # the column of the fused product where the gates' logits begin
         if self.gate_name:
@@ -108,9 +171,42 @@ class AttentionMixer(Part):
         self.position.bind(read, runtime)
 
     def cache_need(self):
+        if self.flex:
+            return PagedNeed(self.num_kv_heads, self.head_dim, self.cache_window,
+                             value_dim=self.value_dim if self.value_dim != self.head_dim else None,
+                             keep_first=self.cache_keep_first if self.cache_window else 0)
         return PagedNeed(self.num_kv_heads, self.head_dim, self.window)
 
+    def forward_inner(self, x, step, cache, writes_cache: bool, out: torch.Tensor, out_scale: float = 1.0) -> torch.Tensor:
+        """The concatenated heads (gated, times `out_scale`) into `out` [rows, heads * value_dim], which may be a column
+        slice of a wider tensor: what the out projection `w_out` is applied to."""
+        if not self.flex:
+            raise NotImplementedError("the concatenated heads of this combination of options are not handed out")
+        R, dt, dev = x.shape[0], x.dtype, x.device
+        Hq, Hk, D, VD = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
+        status = self.runtime.status
+        qkv = linear(self.runtime, x, self.w_qkv)
+        q = torch.empty(R, Hq, D, dtype=dt, device=dev)
+        table = step.block_tables[cache.group]
+        inv_freq, rot = self.position.fused_rotary()
+        own = writes_cache and not self.borrows_keys
+        ops.qkv_rotate_store(qkv, self.col["q"], self.col["k"] if own else -1, self.col["v"] if own else -1, inv_freq, rot,
+                             self.inv_freq_v, step.positions, step.req_of_row, table, cache.page_size, q,
+                             cache.k if own else None, cache.v if own else None, Hq, Hk, D, VD, status)
+        gate = qkv[:, self.col["gate"]:] if self.entry_gate_name else None
+        fast = self.runtime.attention_kernels
+        if fast is not None and hasattr(fast, "attention_flex") and fast.attention_flex(self, q, cache, table, step, gate,
+                                                                                       qkv.stride(0), out_scale, out):
+            return out
+        return ops.attention_flex(q, cache.k, cache.v, table, cache.page_size, step.req_of_row, step.positions, self.scale,
+                                  self.softcap, self.window, self.keep_first, self.inv_freq_v, gate, qkv.stride(0), out_scale,
+                                  out, status)
+
     def forward(self, x, step, cache, writes_cache: bool = True):
+        if self.flex:
+            o = torch.empty(x.shape[0], self.out_dim, dtype=x.dtype, device=x.device)
+            self.forward_inner(x, step, cache, writes_cache, o)
+            return linear(self.runtime, o, self.w_out, out_dtype=torch.float32, defer=True)
         R, dt, dev = x.shape[0], x.dtype, x.device
         Hq, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
         status = self.runtime.status

@@ -13,7 +13,8 @@ Interfaces (duck-typed; the base classes below document them and hold the shared
   PositionEncoding  fused_rotary() -> (inv_freq, rotary_dim) | None      what the fused q/k kernel can apply itself
                   apply(q, k, positions) -> None                         in place on [R, heads, D], else
   Mixer           weight_specs(present) -> [TensorSpec];  bind(read, runtime);
-                  cache_need() -> PagedNeed | SlotNeed | None
+                  cache_need() -> PagedNeed | SlotNeed | None, or a tuple of them for a mixer that keeps several
+                  things (its `cache` is then the tuple of what the manager made for each)
                   forward(x, step, cache, writes_cache=True) -> branch output
   FeedForward     weight_specs(present);  bind(read, runtime);
                   forward(x, step) -> branch output
@@ -123,6 +124,8 @@ class PagedNeed:
     head_dim: int
     window: int | None = None
     values: bool = True         # False: nothing is stored beside the keys (the site's `v` is its `k`)
+    value_dim: int | None = None    # size of a value a head where it differs from a key's (None: head_dim)
+    keep_first: int = 0         # with a window: positions below this stay readable for good, so their pages are kept
 
 
 @dataclass(frozen=True)

@@ -1,7 +1,8 @@
 """The decoder built from a `ModelSpec`: embedding, the scheduled layers, final norm, head.
 
-  h = embed[tokens]; for each site of the schedule: run its layer on its cache; h = final_norm(h);
+  h = embed[tokens] (times the spec's embedding scale); for each site of the schedule: run its layer on its cache; h = final_norm(h);
   logits = h @ head^T in 32-bit, head = the embedding when tied   (engine/models/lfm2_moe/ref.py:218-241)
+  with a soft cap c in the spec: logits <- c tanh(logits / c)
 
 The model owns no cache: `cache_needs()` tells the cache manager what every site needs and `forward` is
 given the per-site caches it made. It computes the final norm and the head for the wanted rows only.
@@ -49,6 +50,10 @@ class DecoderModel:
         """Check `weights` (a FolderWeights or DictWeights) against what the parts read, then bind every part."""
         s = self.spec
         present = weights.present()
+        for layer in self.layers:           # a size that only a stored tensor's shape gives is read before the check
+            for part in layer.parts:
+                if hasattr(part, "shapes_from"):
+                    part.shapes_from(weights.shape_of)
         specs = self.weight_specs(present)
         ignored = set(s.ignored_names)
         weights.check(specs, ignore=(lambda n: n in ignored) if ignored else None)
@@ -120,7 +125,7 @@ class DecoderModel:
     def forward(self, step: StepContext, site_caches: list) -> torch.Tensor:
         rt = self.runtime
         residual = torch.empty(step.n_rows, self.hidden_size, dtype=torch.float32, device=rt.device)
-        ops.embed_rows(self.embedding, step.token_ids, residual, rt.status)
+        ops.embed_rows(self.embedding, step.token_ids, residual, rt.status, self.spec.embedding_scale)
         pending = None
         ranges = SETTINGS.is_set("NVTX")             # named ranges for profilers: the step, and each layer in run order
         if ranges:
@@ -145,6 +150,8 @@ class DecoderModel:
                 torch.cuda.nvtx.range_push("final norm + head")
             n = self.final_norm.add_norm(residual, pending, gather=step.out_rows, n_out=step.n_out)
             out = linear(rt, n, self.head, out_dtype=torch.float32)
+            if self.spec.logit_softcap:
+                ops.softcap(out, float(self.spec.logit_softcap))
             if ranges:
                 torch.cuda.nvtx.range_pop()
             return out

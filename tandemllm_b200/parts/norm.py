@@ -121,6 +121,40 @@ class DynamicTanh(Part):
         return out, out32
 
 
+@register_part("norm", "layernorm")
+class LayerNorm(Part):
+    """Layer norm with weight and bias: out = (x - mean) / sqrt(var + eps) * w + b, var the mean of the squared deviations,
+    all in 32-bit. Tensors: `<name>` (w) and `<name>.b`, where `<name>` is the prefix without its last dot."""
+    graph_safe = True
+
+    def __init__(self, spec, prefix: str = "", size: int = 0, **_):
+        super().__init__(spec, prefix)
+        self.size = size
+        self.eps = float(spec["eps"])
+        self.name = prefix[:-1] if prefix.endswith(".") else prefix
+        self.weight = self.bias = None
+
+    def weight_specs(self, present=None):
+        return [TensorSpec(self.name, (self.size,), role="vector", init="ones"),
+                TensorSpec(self.name + ".b", (self.size,), role="vector", init="bias")]
+
+    def bind(self, read, runtime):
+        self.runtime = runtime
+        self.weight = runtime.vector(read(self.name))
+        self.bias = runtime.vector(read(self.name + ".b"))
+
+    def add_norm(self, residual: torch.Tensor, delta, out: torch.Tensor | None = None,
+                 gather: torch.Tensor | None = None, n_out: int | None = None, want32: bool = False,
+                 route: dict | None = None):
+        if route is not None or want32:
+            raise NotImplementedError("a router or unrounded rows from the layer norm kernel")
+        rows = residual.shape[0] if gather is None else (n_out if n_out is not None else gather.shape[0])
+        if out is None:
+            out = torch.empty(rows, self.size, dtype=self.runtime.dtype, device=residual.device)
+        g = gather[:rows] if gather is not None else None
+        return ops.add_layernorm(residual, delta, self.weight, self.bias, self.eps, out, g)
+
+
 @register_part("norm", "unit_rms")
 class UnitRMS(Part):
     """x / sqrt(mean(x^2) + eps) without a weight: what a mixer names for q and k that are only brought to unit root

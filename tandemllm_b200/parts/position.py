@@ -5,6 +5,11 @@ rotated part share a frequency: x' = x cos + rotate_half(x) sin with rotate_half
 (engine/models/lfm2_moe/ref.py:84, 111-120). The frequencies are computed here once, in 32-bit, by the
 reference's expression; the angles, sines and cosines are computed in the kernel in 32-bit per row.
 
+With `scaling` = {factor, low, high, original} the long wavelengths are slowed (the Llama 3.1 rule): with wavelength
+l = 2 pi / f, f stays where l < original / high, becomes f / factor where l > original / low, and between the two is
+(1 - s) f / factor + s f with s = (original / l - low) / (high - low). With `precise` (or a scaling) the frequencies are
+formed in 64-bit and rounded once.
+
 `rope_pairs`: the interleaved layout: entries 2i and 2i + 1 of the rotated part are a pair, (u, v) at position p becomes
 (u cos a - v sin a, v cos a + u sin a) with a = p * theta^(-2i/d), for the first d = `rotary_dim` entries (the rest pass).
 The frequencies are formed once in 64-bit and rounded to 32-bit; angles, sines and cosines are 32-bit in the kernel. A
@@ -17,6 +22,8 @@ through `apply(q, k, positions)` between the norm and the cache write.
 """
 
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -33,13 +40,27 @@ class RotaryNeox(Part):
         self.rotary_dim = int(spec.get("rotary_dim") or head_dim)
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= head_dim:
             raise ValueError(f"rotary size {self.rotary_dim} for head size {head_dim}: an even size up to the head size")
+        self.scaling = spec.get("scaling")
+        self.precise = bool(spec.get("precise", False)) or self.scaling is not None
         self.inv_freq = None
+
+    def frequencies(self) -> torch.Tensor:
+        d = self.rotary_dim
+        if not self.precise:
+            return 1.0 / (self.theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+        f = self.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)
+        if self.scaling:
+            s = self.scaling
+            factor, low, high, orig = (float(s[k]) for k in ("factor", "low", "high", "original"))
+            wavelength = 2.0 * math.pi / f
+            blend = (orig / wavelength - low) / (high - low)
+            mid = (1.0 - blend) * f / factor + blend * f
+            f = torch.where(wavelength < orig / high, f, torch.where(wavelength > orig / low, f / factor, mid))
+        return f.to(torch.float32)
 
     def bind(self, read, runtime):
         self.runtime = runtime
-        d = self.rotary_dim
-        inv = 1.0 / (self.theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
-        self.inv_freq = inv.to(runtime.device)
+        self.inv_freq = self.frequencies().to(runtime.device)
 
     def fused_rotary(self):
         return self.inv_freq, self.rotary_dim

@@ -98,6 +98,11 @@ class FolderWeights:
     def check(self, expected: list[TensorSpec], ignore: Callable[[str], bool] | None = None) -> None:
         audit(expected, self.stored, self.names, self.folder, ignore)
 
+    def shape_of(self, name: str) -> tuple[int, ...] | None:
+        """The stored shape of a tensor, or None when the folder has none of that name (a part whose configuration leaves
+        a size to its tensors asks before it says what it reads)."""
+        return tuple(self.stored[self.names[name]].shape) if name in self.names else None
+
     def read(self, name: str) -> torch.Tensor:
         st = self.stored[self.names[name]]
         t = read_tensor(st)
@@ -116,6 +121,9 @@ class DictWeights:
     def check(self, expected: list[TensorSpec], ignore: Callable[[str], bool] | None = None) -> None:
         stored = {n: StoredTensor(n, "<memory>", "", tuple(t.shape), 0, 0) for n, t in self.tensors.items()}
         audit(expected, stored, {n: n for n in stored}, "<memory>", ignore)
+
+    def shape_of(self, name: str) -> tuple[int, ...] | None:
+        return tuple(self.tensors[name].shape) if name in self.tensors else None
 
     def read(self, name: str) -> torch.Tensor:
         t = self.tensors[name]
