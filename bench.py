@@ -19,6 +19,8 @@ requests at a context of 8192 tokens. A "step" is one decode step of the whole b
              CUDA graphs
 
 `--design puripel` does the same for Puripel beside an LFM2 MoE model of short-convolution and attention layers.
+`--design sebilorn` does the same for Sebilorn beside an LFM2 model of short-convolution and attention layers with dense
+feed-forwards.
 `--design sifupel` measures the Sifupel design beside the closest existing model (an LFM2 configuration of attention layers
 and dense feed-forwards only) at a few equal layer sizes: prefill and decode throughput, and every launch summed by kernel
 family with its fraction of the measured peak (its own line; the default workload and line are untouched).
@@ -370,7 +372,12 @@ class LaunchTimer:
                 "tl_latent_prepare": "latent norm + rotary + cache write", "tl_rmsnorm_rows": "latent norm + rotary + cache write",
                 "tl_head_linear": "products a head", "tl_head_linear_mma": "products a head", "tl_attention_latent_mma": "latent attention", "tl_attention_latent": "latent attention",
                 "tl_add_normed": "norm behind a branch + residual add (+ next norm)", "tl_add_vector": "vector onto the stream", "tl_row_dot": "gate logit a row",
-                "tl_ssm_decode": "conv + state-space recurrence + gate + norm (decode)"}.get(name, name)
+                "tl_ssm_decode": "conv + state-space recurrence + gate + norm (decode)",
+                "tl_recurrence_scan": "matrix-state recurrence", "tl_recurrence_chunks": "matrix-state recurrence",
+                "tl_group_norm_gate": "norm in parts + gate",
+                "tl_qkv_rotate_store": "rotary (+ turned values) + cache write", "tl_attention_flex": "attention",
+                "tl_attention_flex_mma": "attention", "tl_add_layernorm": "residual add + layer norm",
+                "tl_softcap": "logit cap"}.get(name, name)
 
     def __enter__(self):
         torch = self.torch
@@ -748,6 +755,176 @@ def puripel_compare(a) -> int:
     return 0
 
 
+SEBILORN_SIZES = {
+    "1k": dict(width=1024, layers=8, vocab=32768, heads=16, kv=4, dim=64, vdim=64, window=512, keep=4, ff=4096,
+               delta_heads=16, delta_dim=64, lin_heads=16, lin_dim=64, lin_vdim=64),
+    "2k": dict(width=2048, layers=12, vocab=65536, heads=16, kv=4, dim=128, vdim=128, window=1024, keep=4, ff=8192,
+               delta_heads=16, delta_dim=128, lin_heads=16, lin_dim=128, lin_vdim=128),
+}
+
+
+def sebilorn_compare(a) -> int:
+    """Sebilorn beside the closest existing model at equal width, depth, vocabulary, heads and feed-forward weight count: an
+    LFM2 model of short-convolution and attention layers with dense SwiGLU feed-forwards (attention where Sebilorn attends,
+    a short convolution where Sebilorn carries a matrix state). Sebilorn's layers repeat (windowed attention that owns its
+    keys, windowed attention that borrows them, attention beside the delta rule, decayed linear attention). Random weights.
+    For each: a prompt of `--prefill-tokens` tokens, decode steps of `--batch` requests at a context of twice the window
+    (device-timed, from CUDA graphs where the engine takes them), and one eager decode step and one prefill with every launch
+    timed and summed by kernel family. Work: attention 2 (dim + vdim) flops a visible (row, key, head) and, decoding, the
+    bytes of the visible cached rows; the recurrences 10 (delta rule) or 6 (fixed decay) 32-bit flops a (row, head, key,
+    value) on the CUDA cores and, decoding, the states read and written."""
+    import torch
+
+    from tandemllm_b200.config import Lfm2MoeConfig, SebilornConfig
+    from tandemllm_b200.engine import Engine, EngineArgs, StepEntry
+    from tandemllm_b200.kernels import ops
+    from tandemllm_b200.sampling import SamplingParams
+    pk = peaks()
+    tokens, batch = a.prefill_tokens, a.batch
+    elem = 2 if a.dtype == "bfloat16" else 4
+    out = []
+    for label in (a.design_sizes.split(",") if a.design_sizes else SEBILORN_SIZES):
+        z = SEBILORN_SIZES[label]
+        W, L, V, H, G, D, VD, win, keep, ff = (z[k] for k in ("width", "layers", "vocab", "heads", "kv", "dim", "vdim", "window",
+                                                              "keep", "ff"))
+        mlp = {"kind": "dense", "ff": ff}
+        rot = {"base": 500000.0, "dims": D, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+        att = {"heads": H, "kv_heads": G, "dim": D, "vdim": VD, "scale": D ** -0.5, "softcap": 50.0, "rot": rot,
+               "mask": {"size": win, "keep_first": keep}}
+        left = {"heads": H, "kv_heads": G, "dim": D, "vdim": VD, "scale": D ** -0.5, "rot": {"base": 1e6, "dims": D}}
+        layers = []
+        for i in range(L):
+            k = i % 4
+            if k == 0:
+                layers.append({"type": "attention", "mixer": dict(att), "mlp": mlp})
+            elif k == 1:
+                layers.append({"type": "attention", "mixer": dict(att, kv_from=i - 1), "mlp": mlp})
+            elif k == 2:
+                layers.append({"type": "parallel", "mlp": mlp,
+                               "mixer": {"left": left, "right": {"heads": z["delta_heads"], "dim": z["delta_dim"]},
+                                         "left_scale": 0.8, "right_scale": 0.5}})
+            else:
+                Hl = z["lin_heads"]
+                layers.append({"type": "lightning", "mlp": mlp,
+                               "mixer": {"heads": Hl, "dim": z["lin_dim"], "vdim": z["lin_vdim"],
+                                         "decay": [1.0 - 2.0 ** (-3 - 5 * h / max(Hl - 1, 1)) for h in range(Hl)]}})
+        seb = SebilornConfig.from_dict({"architecture": "Sebilorn", "vocab": V, "width": W, "norm": {"eps": 1e-5},
+                                        "embedding": {"scale": W ** 0.5}, "logit_softcap": 30.0, "layers": layers})
+        inter = (2 * ff // 3 + 255) // 256 * 256
+        lfm = Lfm2MoeConfig.from_dict(dict(
+            CONFIG_8B, vocab_size=V, hidden_size=W, intermediate_size=inter, num_hidden_layers=L, num_attention_heads=H,
+            num_key_value_heads=G, head_dim=D, num_dense_layers=L,
+            layer_types=["full_attention" if i % 4 < 3 else "conv" for i in range(L)]))
+        context = 2 * win
+        n_own, n_borrow, n_par, n_lin = ((L - k + 3) // 4 for k in range(4))
+        row = {"sizes": dict(z, label=label), "prefill_tokens": tokens, "batch": batch, "context": context}
+        for name, cfg in (("sebilorn", seb), ("lfm2_conv_attention_dense", lfm)):
+            room = max(context, tokens) + 4 * a.steps + 64
+            engine = Engine.from_config(cfg, seed=0, args=EngineArgs(
+                dtype=a.dtype, max_len=room, parallel=batch, block_size=16, max_batched_tokens=max(tokens, batch),
+                chunk_size=tokens, graph=a.graph == "on"))
+            for sc in engine.cache.site_cache:
+                for c in (sc if isinstance(sc, tuple) else (sc,)):
+                    if hasattr(c, "k") and c.k is not None:
+                        c.k.normal_(0, 0.5)
+                        if c.v is not c.k:
+                            c.v.normal_(0, 0.5)
+            g = torch.Generator().manual_seed(1)
+            fn = engine.step_function
+
+            def prefill_once():
+                engine.admit("prefill")
+                prompt = torch.randint(0, V, (tokens,), generator=g).tolist()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                engine.step([StepEntry("prefill", prompt, [tokens - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                engine.release("prefill")
+                return e0.elapsed_time(e1)
+            prefill_once()
+            pre_ms = statistics.median(prefill_once() for _ in range(3))
+            timer = LaunchTimer()
+            with timer:
+                prefill_once()
+                pre_table = timer.table()
+            greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
+            reqs = [start_with_context(engine, torch.randint(0, V, (context,), generator=g).tolist(),
+                                       SamplingParams(**vars(greedy))) for _ in range(batch)]
+            fn.check_status = False
+            toks = torch.randint(0, V, (3 * a.steps + a.warmup + 4, batch), generator=g).tolist()
+            picked = torch.empty(batch, dtype=torch.int32, device=engine.device)
+
+            def one(i):
+                ops.argmax(fn.run([StepEntry(r.request_id, [toks[i][j]], [0]) for j, r in enumerate(reqs)]), picked)
+            for i in range(a.warmup):
+                one(i)
+            torch.cuda.synchronize()
+            regions = []
+            for rep in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(a.warmup + rep * a.steps, a.warmup + (rep + 1) * a.steps):
+                    one(i)
+                e1.record()
+                torch.cuda.synchronize()
+                regions.append(e0.elapsed_time(e1) / a.steps)
+            dec_ms = statistics.median(regions)
+            kept, fn.use_graphs = fn.use_graphs, False
+            one(3 * a.steps + a.warmup)
+            with timer:
+                one(3 * a.steps + a.warmup + 1)
+                dec_table = timer.table()
+            fn.use_graphs = kept
+            fn.check_status = True
+            fn.raise_on_fault()
+            for t in (pre_table, dec_table):
+                for r in t.values():
+                    r["ms"] = round(r["ms"], 4)
+            entry = {"prefill": {"ms": round(pre_ms, 3), "tok_s": round(tokens / pre_ms * 1e3, 1), "families": pre_table},
+                     "decode": {"ms_per_step": round(dec_ms, 4), "tok_s": round(batch / dec_ms * 1e3, 1),
+                                "weight_bytes_per_step": engine.model.decode_bytes(batch)["total"], "families": dec_table}}
+            entry["decode"]["frac_hbm_weights_only"] = round(entry["decode"]["weight_bytes_per_step"] / dec_ms / 1e6 / pk["hbm_gbs"], 4)
+            if name == "sebilorn":
+                seen_win = sum(min(i + 1, win) + min(keep, max(0, i + 1 - win)) for i in range(tokens))
+                seen_all = tokens * (tokens + 1) // 2
+                att_flops = 2.0 * (D + VD) * H * (seen_win * (n_own + n_borrow) + seen_all * n_par)
+                vis = min(context, win + keep)
+                att_bytes = float(elem) * batch * G * (D + VD) * (vis * (n_own + n_borrow) + context * n_par)
+                Hd, Dd, Hl, Dl, Vl = z["delta_heads"], z["delta_dim"], z["lin_heads"], z["lin_dim"], z["lin_vdim"]
+                rec_flops = tokens * (10.0 * Hd * Dd * Dd * n_par + 6.0 * Hl * Dl * Vl * n_lin)
+                rec_bytes = 8.0 * batch * (Hd * Dd * Dd * n_par + Hl * Dl * Vl * n_lin)
+            else:
+                n_att = sum(1 for i in range(L) if i % 4 < 3)
+                att_flops = 4.0 * D * H * (tokens * (tokens + 1) // 2) * n_att
+                att_bytes = float(elem) * batch * G * 2 * D * context * n_att
+                rec_flops = rec_bytes = 0.0
+            for fam, flops, nbytes, peak in (("attention", att_flops, att_bytes, pk["bf16_tflops"]),
+                                             ("matrix-state recurrence", rec_flops, rec_bytes, None)):
+                if fam in pre_table and flops:
+                    rate = flops / pre_table[fam]["ms"] / 1e9
+                    pre_table[fam]["TFLOPs"] = round(rate, 2)
+                    if peak and a.dtype == "bfloat16":
+                        pre_table[fam]["frac_of_measured_bf16"] = round(rate / peak, 4)
+                if fam in dec_table and nbytes:
+                    rate = nbytes / dec_table[fam]["ms"] / 1e6
+                    dec_table[fam]["GBps"] = round(rate, 1)
+                    dec_table[fam]["frac_hbm"] = round(rate / pk["hbm_gbs"], 4)
+            row[name] = entry
+            for r in reqs:
+                r.num_computed = engine.cache.length_of(r.request_id)
+                engine.scheduler.abort(r)
+            del engine, fn, reqs
+            torch.cuda.empty_cache()
+        out.append(row)
+    print(json.dumps({"design_compare": "sebilorn beside lfm2 (short convolution and attention layers, dense feed-forwards)",
+                      "dtype": a.dtype, "peaks": pk,
+                      "data": "synthetic: random weights, uniform random token ids, random cached rows as context",
+                      "rows": out}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -782,16 +959,16 @@ def main() -> int:
                     help="programmatic dependent launch between the kernels (for comparison; ordinary launches by default)")
     ap.add_argument("--profile", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--design", choices=("sifupel", "puripel"),
+    ap.add_argument("--design", choices=("sifupel", "puripel", "sebilorn"),
                     help="measure this design beside the closest existing model at equal layer sizes (its own line)")
     ap.add_argument("--design-sizes", default="", help="--design: which of " + ", ".join(DESIGN_SIZES) + " (sifupel) or "
-                    + ", ".join(PURIPEL_SIZES) + " (puripel) (default: all)")
+                    + ", ".join(PURIPEL_SIZES) + " (puripel) or " + ", ".join(SEBILORN_SIZES) + " (sebilorn) (default: all)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
     if a.design:
         a.warmup = max(a.warmup, 3)
-        return puripel_compare(a) if a.design == "puripel" else design_compare(a)
+        return {"puripel": puripel_compare, "sebilorn": sebilorn_compare}.get(a.design, design_compare)(a)
     if a.gpus != 1:
         print(json.dumps({"error": f"this engine runs on one GPU; --gpus {a.gpus} is not implemented", "n_gpus": a.gpus}))
         return 2
