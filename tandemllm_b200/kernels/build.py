@@ -38,7 +38,7 @@ LIBRARIES: dict[str, list[str]] = {
              "attention_headmix.cu", "attention_latent.cu", "attention_flex.cu", "ssm.cu", "recurrence.cu", "layernorm.cu", "post_norm.cu", "moe_route.cu", "sampling.cu", "graphs.cu"],
     # the tcgen05 / TMA kernels of the bfloat16 path; a 32-bit run never builds or loads them
     "tensorcore": ["tc_gemm.cu", "tc_gemm_pair.cu", "attention_mma.cu", "attention_tc.cu", "attention_headmix_mma.cu",
-                   "attention_latent_mma.cu", "head_linear_mma.cu", "gemm_skinny_mma.cu"],
+                   "attention_latent_mma.cu", "attention_flex_mma.cu", "head_linear_mma.cu", "gemm_skinny_mma.cu"],
 }
 HEADERS = ["common.cuh", "route.cuh", "attention_noalloc.h", "tma.cuh"]
 

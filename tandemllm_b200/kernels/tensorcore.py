@@ -120,6 +120,15 @@ def lib():
                                                c_void_p, ctypes.c_float, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int,
                                                c_int, c_int, c_void_p, c_void_p]
         l.tl_attention_headmix_mma.restype = c_int
+        l.tl_attention_flex_mma_supported.argtypes = [c_int, c_int, c_int, c_int]
+        l.tl_attention_flex_mma_supported.restype = c_int
+        l.tl_attention_flex_mma_tile_rows.argtypes = [c_int, c_int]
+        l.tl_attention_flex_mma_tile_rows.restype = c_int
+        l.tl_attention_flex_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                            c_void_p, ctypes.c_float, ctypes.c_float, c_int, c_int, c_void_p, c_void_p, c_longlong,
+                                            ctypes.c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                            c_void_p]
+        l.tl_attention_flex_mma.restype = c_int
         l.tl_gemm_skinny_supported.argtypes = [c_int, c_int, c_int, c_longlong, c_longlong]
         l.tl_gemm_skinny_supported.restype = c_int
         l.tl_gemm_skinny_mma.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int,
@@ -533,6 +542,37 @@ class TensorCore:
         return True
 
 
+def _attention_flex(self, part, q, cache, table, step, gate, ld_gate: int, out_scale: float, out) -> bool:
+    """Attention with capped scores, kept first tokens, values of their own size, a turned output and an entry-wise gate
+    (whatever of these `part` has) on the tensor cores; False when the sizes are not the kernel's (keys and values of 64 or
+    128 entries, groups up to 64, bfloat16): the caller then uses the CUDA-core kernel. Requests that bring a row or a few
+    go to the form that splits each key tile among the warps, the others to tiles of 64 M rows."""
+    R, Hq, D = q.shape
+    Hk, VD = cache.k.shape[1], cache.v.shape[-1]
+    if q.dtype != torch.bfloat16 or not lib().tl_attention_flex_mma_supported(Hq, Hk, D, VD):
+        return False
+    if out.data_ptr() % 4 or out.stride(0) % 2 or out.stride(1) != 1:
+        return False
+    G = Hq // Hk
+    tile_rows = lib().tl_attention_flex_mma_tile_rows(Hq, Hk)
+    small_rows = 16 // G
+    if step.max_rows_per_request == 1 and small_rows >= 1:
+        lists = [(self.query_tiles(step, tile_rows), 1)]
+    elif small_rows >= 1:
+        big, small, small_max = self._split_tiles(step, tile_rows, small_rows)
+        lists = [(t, n) for t, n in ((big, min(tile_rows, step.max_rows_per_request)), (small, small_max)) if t is not None]
+    else:
+        lists = [(self.query_tiles(step, tile_rows), min(tile_rows, step.max_rows_per_request))]
+    for tiles, most in lists:
+        code = lib().tl_attention_flex_mma(
+            q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
+            cache.k.shape[0], tiles.data_ptr(), tiles.shape[0], int(most), step.positions.data_ptr(), float(part.scale),
+            float(part.softcap or 0.0), int(part.window or 0), int(part.keep_first or 0), ops.ptr(part.inv_freq_v), ops.ptr(gate),
+            int(ld_gate), float(out_scale), out.data_ptr(), out.stride(0), R, Hq, Hk, D, VD, self.status.data_ptr(), ops.stream())
+        _check(code, "attention_flex_mma")
+    return True
+
+
 def _split_tiles(self, step, big_rows: int, small_rows: int):
     """(tiles of requests that bring more than `small_rows` rows, cut into `big_rows` rows; one tile for each of the other
     requests), each int32 [n, 3] = (request, first row, rows) on the device, or None. Kept on the step."""
@@ -590,6 +630,7 @@ def _prompt_attention(self, q, cache, table, step, scale, window, out, runtime) 
 
 
 TensorCore._split_tiles = _split_tiles
+TensorCore.attention_flex = _attention_flex
 TensorCore._prompt_attention = _prompt_attention
 
 

@@ -115,6 +115,8 @@ ATTN_CASES = {
     "a window of one": (6, 1, 8, 6, 0.5, 4, None, (1, 0), 30.0),
     "wide values": (2, 1, 128, 256, 0.07, 96, (2.0, 1.0, 2.0, 128), (33, 5), 15.0),
     "kept tokens past a page": (4, 4, 32, 32, 0.2, 16, None, (20, 19), None),
+    "keys of 128, values of 64": (4, 2, 128, 64, 0.09, 64, None, (40, 3), 20.0),
+    "three heads a kv head, more kept tokens than a key tile": (6, 2, 64, 128, 0.12, 64, (8.0, 1.0, 4.0, 64), (30, 70), 35.0),
 }
 
 
@@ -173,7 +175,7 @@ def test_attention_sees_its_window_and_its_kept_first_tokens_and_nothing_else(ca
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,D,VD,dims", [(3, 3, 12, 20, 4), (8, 2, 64, 64, 64), (4, 2, 64, 128, 32), (2, 1, 32, 32, 16)])
+@pytest.mark.parametrize("H,G,D,VD,dims", [(3, 3, 12, 20, 4), (8, 2, 64, 64, 64), (4, 2, 64, 128, 32), (2, 1, 32, 32, 16), (4, 1, 128, 128, 64)])
 def test_gated_attention_reaches_a_far_key_among_hundreds(dtype, H, G, D, VD, dims):
     """The attention of a side-by-side mixer on its own: causal over all keys, an entry-wise sigmoid gate, no turned values.
     One key hundreds of tokens back stands out; prompts, portions and decoding."""
