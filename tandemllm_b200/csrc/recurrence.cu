@@ -14,6 +14,14 @@
 // shuffles among P lanes and no thread waits for another inside a token. Eight tokens at a time are staged in shared
 // memory: a warp a token forms the activations, decays and the unit key once (never once a thread). Everything is
 // 32-bit. A row's result depends on its request's earlier rows only, added in a fixed order.
+//
+// Steps that bring long portions run two kernels instead: one warp a (row, head) forms the activations, decays and unit
+// keys of all rows side by side into a scratch tensor, and the scan fetches them (and the values) a few tokens ahead
+// through a ring of cp.async stages that a warp of its own keeps filled, so that nothing but the state's own chain of
+// additions is left in the computing warps' loop. The
+// blocks shrink (down to a warp of a few value columns) until the grid fills the GPU: the chain's length in time is the
+// same for every block size, so more and smaller blocks only shorten the step. The arithmetic of a token is the same in
+// both forms.
 #include "common.cuh"
 
 namespace tl {
@@ -62,14 +70,16 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
       s[4 * m + c] = (owns && i < D) ? S[(long long)i * VD + j] : 0.f;
     }
 
-  for (int t0 = r0; t0 < r1; t0 += REC_TOKENS) {
-    const int nt = min(REC_TOKENS, r1 - t0);
+  const int chunk_tokens = min(REC_TOKENS, (int)(blockDim.x >> 5));      // a warp a token
+  for (int t0 = r0; t0 < r1; t0 += chunk_tokens) {
+    const int nt = min(chunk_tokens, r1 - t0);
     __syncthreads();                      // the chunk before has been read
     if (warp < nt) {
-      const float* row = proj + (long long)(t0 + warp) * ld + (long long)h * D;
-      const float* vrow = proj + (long long)(t0 + warp) * ld + v_col + (long long)h * VD;
-      float* tq = s_q + warp * Dp;
-      float* tk = s_k + warp * Dp;
+      const int tw = warp;
+      const float* row = proj + (long long)(t0 + tw) * ld + (long long)h * D;
+      const float* vrow = proj + (long long)(t0 + tw) * ld + v_col + (long long)h * VD;
+      float* tq = s_q + tw * Dp;
+      float* tk = s_k + tw * Dp;
       float ss = 0.f;
       for (int i = lane; i < Dp; i += 32) {
         float qv = 0.f, kv = 0.f;
@@ -88,7 +98,7 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
       if (DELTA) {
         ss = warp_sum(ss);
         const float inv = 1.f / sqrtf(ss + key_eps);
-        const float* wrow = wl + (long long)(t0 + warp) * ld_w + (long long)h * D;
+        const float* wrow = wl + (long long)(t0 + tw) * ld_w + (long long)h * D;
         for (int i = lane; i < Dp; i += 32) {
           float d = 0.f, u = 0.f, au = 0.f;
           if (i < D) {
@@ -96,15 +106,15 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
             u = tk[i] * inv;
             au = sigmoidf_(row[a_col + i] + a_bias[h * D + i]) * u;
           }
-          s_d[warp * Dp + i] = d;
-          s_u[warp * Dp + i] = u;
-          s_au[warp * Dp + i] = au;
+          s_d[tw * Dp + i] = d;
+          s_u[tw * Dp + i] = u;
+          s_au[tw * Dp + i] = au;
         }
       }
       for (int c = lane; c < cols_per_block; c += 32) {
         float vv = col0 + c < VD ? vrow[col0 + c] : 0.f;
         if (silu_inputs) vv = siluf_(vv);
-        s_v[warp * cols_per_block + c] = vv;
+        s_v[tw * cols_per_block + c] = vv;
       }
     }
     __syncthreads();
@@ -112,20 +122,21 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
       const float4* q4 = reinterpret_cast<const float4*>(s_q + t * Dp);
       const float4* k4 = reinterpret_cast<const float4*>(s_k + t * Dp);
       const float vj = jl < cols_per_block ? s_v[t * cols_per_block + jl] : 0.f;
-      float o = 0.f;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
       if (DELTA) {
         const float4* d4 = reinterpret_cast<const float4*>(s_d + t * Dp);
         const float4* u4 = reinterpret_cast<const float4*>(s_u + t * Dp);
         const float4* au4 = reinterpret_cast<const float4*>(s_au + t * Dp);
-        float us = 0.f;
+        float us0 = 0.f, us1 = 0.f, us2 = 0.f, us3 = 0.f;      // four short chains of additions instead of one long one
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
           const float4 u = u4[part + P * m];
-          us = fmaf(u.x, s[4 * m], us);
-          us = fmaf(u.y, s[4 * m + 1], us);
-          us = fmaf(u.z, s[4 * m + 2], us);
-          us = fmaf(u.w, s[4 * m + 3], us);
+          us0 = fmaf(u.x, s[4 * m], us0);
+          us1 = fmaf(u.y, s[4 * m + 1], us1);
+          us2 = fmaf(u.z, s[4 * m + 2], us2);
+          us3 = fmaf(u.w, s[4 * m + 3], us3);
         }
+        float us = (us0 + us1) + (us2 + us3);
         for (int off = P >> 1; off > 0; off >>= 1) us += __shfl_xor_sync(0xffffffffu, us, off);
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
@@ -134,10 +145,10 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
           s[4 * m + 1] = fmaf(d.y, s[4 * m + 1], fmaf(-au.y, us, k.y * vj));
           s[4 * m + 2] = fmaf(d.z, s[4 * m + 2], fmaf(-au.z, us, k.z * vj));
           s[4 * m + 3] = fmaf(d.w, s[4 * m + 3], fmaf(-au.w, us, k.w * vj));
-          o = fmaf(s[4 * m], q.x, o);
-          o = fmaf(s[4 * m + 1], q.y, o);
-          o = fmaf(s[4 * m + 2], q.z, o);
-          o = fmaf(s[4 * m + 3], q.w, o);
+          o0 = fmaf(s[4 * m], q.x, o0);
+          o1 = fmaf(s[4 * m + 1], q.y, o1);
+          o2 = fmaf(s[4 * m + 2], q.z, o2);
+          o3 = fmaf(s[4 * m + 3], q.w, o3);
         }
       } else {
 #pragma unroll
@@ -147,15 +158,210 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
           s[4 * m + 1] = fmaf(c_h, s[4 * m + 1], k.y * vj);
           s[4 * m + 2] = fmaf(c_h, s[4 * m + 2], k.z * vj);
           s[4 * m + 3] = fmaf(c_h, s[4 * m + 3], k.w * vj);
-          o = fmaf(s[4 * m], q.x, o);
-          o = fmaf(s[4 * m + 1], q.y, o);
-          o = fmaf(s[4 * m + 2], q.z, o);
-          o = fmaf(s[4 * m + 3], q.w, o);
+          o0 = fmaf(s[4 * m], q.x, o0);
+          o1 = fmaf(s[4 * m + 1], q.y, o1);
+          o2 = fmaf(s[4 * m + 2], q.z, o2);
+          o3 = fmaf(s[4 * m + 3], q.w, o3);
         }
       }
+      float o = (o0 + o1) + (o2 + o3);
       for (int off = P >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
       if (part == 0 && owns) y[(long long)(t0 + t) * H * VD + (long long)h * VD + j] = o;
     }
+  }
+  if (write_state && owns) {
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int i = 4 * (part + P * m) + c;
+        if (i < D) S[(long long)i * VD + j] = s[4 * m + c];
+      }
+  }
+}
+
+// One warp a (row, head): what the scan needs of a token, [rows][H][NARR][Dp] = q, k (activated), and for the delta rule
+// d, u, a * u; entries past D are zero. With `vact`, the activated values [rows][H * VD] as well.
+template <bool DELTA>
+__global__ void __launch_bounds__(128) recurrence_prepare_kernel(
+    const float* __restrict__ proj, long long ld, int q_col, int k_col, int v_col, int a_col, const float* __restrict__ wl,
+    long long ld_w, const float* __restrict__ w0, const float* __restrict__ a_bias, float rate, float key_eps, int silu_inputs,
+    float* __restrict__ prep, float* __restrict__ vact, int H, int D, int VD, int Dp, long long pairs) {
+  constexpr int NARR = DELTA ? 5 : 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long idx = (long long)blockIdx.x * 4 + warp;
+  if (idx >= pairs) return;
+  const long long r = idx / H;
+  const int h = (int)(idx - r * H);
+  const float* row = proj + r * ld + (long long)h * D;
+  float* tq = prep + idx * NARR * Dp;
+  float* tk = tq + Dp;
+  float ss = 0.f;
+  for (int i = lane; i < Dp; i += 32) {
+    float qv = 0.f, kv = 0.f;
+    if (i < D) {
+      qv = row[q_col + i];
+      kv = row[k_col + i];
+      if (silu_inputs) {
+        qv = siluf_(qv);
+        kv = siluf_(kv);
+      }
+    }
+    tq[i] = qv;
+    tk[i] = kv;
+    ss = fmaf(kv, kv, ss);
+  }
+  if (DELTA) {
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss + key_eps);
+    const float* wrow = wl + r * ld_w + (long long)h * D;
+    for (int i = lane; i < Dp; i += 32) {
+      float d = 0.f, u = 0.f, au = 0.f;
+      if (i < D) {
+        d = expf(-rate * sigmoidf_(wrow[i] + w0[h * D + i]));
+        u = tk[i] * inv;                  // (this lane wrote it)
+        au = sigmoidf_(row[a_col + i] + a_bias[h * D + i]) * u;
+      }
+      tq[2 * Dp + i] = d;
+      tq[3 * Dp + i] = u;
+      tq[4 * Dp + i] = au;
+    }
+  }
+  if (vact) {
+    const float* vrow = proj + r * ld + v_col + (long long)h * VD;
+    for (int c = lane; c < VD; c += 32) vact[idx * VD + c] = silu_inputs ? siluf_(vrow[c]) : vrow[c];
+  }
+}
+
+__device__ __forceinline__ void rec_cp16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void rec_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// The scan over prepared tokens. Block: cols_per_block * P computing threads (a multiple of 32) and one more warp, the
+// producer, which does nothing but fetch: it keeps STAGES - 1 chunks of TC tokens in flight (each token's NARR * Dp prepared
+// floats, then the chunk's TC * cols_per_block values) and meets the computing warps at one barrier a chunk, when the next
+// chunk has landed and the last one has been read.
+template <bool DELTA, int STAGES>
+__global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kernel(
+    const float* __restrict__ prep, const float* __restrict__ vsrc, long long ld_v, int v_col, const float* __restrict__ head_decay,
+    float* __restrict__ state, long long slot_floats, const int* __restrict__ state_slot, const int* __restrict__ row_start,
+    float* __restrict__ y, int H, int D, int VD, int P, int cols_per_block, int TC, int write_state) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int NARR = DELTA ? 5 : 2;
+  const int Dp = 16 * P, tok_floats = NARR * Dp;
+  const int stage_floats = TC * (tok_floats + cols_per_block);
+  const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols_per_block;
+  const int tid = threadIdx.x, nth = blockDim.x - 32;
+  const bool producer = tid >= nth;
+  const int part = tid % P, jl = tid / P, j = col0 + jl;
+  const bool owns = !producer && j < VD;
+  const int r0 = row_start[b], r1 = row_start[b + 1];
+  if (r1 <= r0) return;
+  float* S = state + (long long)state_slot[b] * slot_floats + (long long)h * D * VD;
+  const float c_h = DELTA ? 0.f : head_decay[h];
+  const int n_chunks = (r1 - r0 + TC - 1) / TC;
+
+  // (the producer's lanes only)
+  auto load = [&](int chunk) {
+    const int lane = tid - nth;
+    const int t0 = r0 + chunk * TC, nt = min(TC, r1 - t0);
+    float* base = sm + (chunk % STAGES) * stage_floats;
+    for (int t = 0; t < nt; ++t) {
+      const float* src = prep + ((long long)(t0 + t) * H + h) * tok_floats;
+      for (int p = 4 * lane; p < tok_floats; p += 128) rec_cp16(base + t * tok_floats + p, src + p);
+      float* vb = base + TC * tok_floats + t * cols_per_block;
+      const float* vs = vsrc + (long long)(t0 + t) * ld_v + v_col + (long long)h * VD + col0;
+      for (int c = lane; c < cols_per_block; c += 32) {
+        if (col0 + c < VD) rec_cp4(vb + c, vs + c);
+        else vb[c] = 0.f;
+      }
+    }
+  };
+  float s[16];
+  if (producer) {
+#pragma unroll
+    for (int s0 = 0; s0 < STAGES - 1; ++s0) {
+      if (s0 < n_chunks) load(s0);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");       // chunk 0 has landed
+  } else {
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int i = 4 * (part + P * m) + c;
+        s[4 * m + c] = (owns && i < D) ? S[(long long)i * VD + j] : 0.f;
+      }
+  }
+  __syncthreads();
+
+  for (int chunk = 0; chunk < n_chunks; ++chunk) {
+    if (producer) {
+      // the stage of chunk - 1 is free (everybody passed the barrier behind it): refill it, then wait for chunk + 1
+      if (chunk + STAGES - 1 < n_chunks) load(chunk + STAGES - 1);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    } else {
+      const int t0 = r0 + chunk * TC, nt = min(TC, r1 - t0);
+      const float* base = sm + (chunk % STAGES) * stage_floats;
+      const float* vb = base + TC * tok_floats;
+      for (int t = 0; t < nt; ++t) {
+        const float4* q4 = reinterpret_cast<const float4*>(base + t * tok_floats);
+        const float4* k4 = q4 + Dp / 4;
+        const float vj = vb[t * cols_per_block + jl];
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+        if (DELTA) {
+          const float4* d4 = k4 + Dp / 4;
+          const float4* u4 = d4 + Dp / 4;
+          const float4* au4 = u4 + Dp / 4;
+          // four short chains of additions instead of one long one: the sum over keys is what the next token waits for
+          float us0 = 0.f, us1 = 0.f, us2 = 0.f, us3 = 0.f;
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const float4 u = u4[part + P * m];
+            us0 = fmaf(u.x, s[4 * m], us0);
+            us1 = fmaf(u.y, s[4 * m + 1], us1);
+            us2 = fmaf(u.z, s[4 * m + 2], us2);
+            us3 = fmaf(u.w, s[4 * m + 3], us3);
+          }
+          float us = (us0 + us1) + (us2 + us3);
+          for (int off = P >> 1; off > 0; off >>= 1) us += __shfl_xor_sync(0xffffffffu, us, off);
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const float4 d = d4[part + P * m], au = au4[part + P * m], k = k4[part + P * m], q = q4[part + P * m];
+            s[4 * m] = fmaf(d.x, s[4 * m], fmaf(-au.x, us, k.x * vj));
+            s[4 * m + 1] = fmaf(d.y, s[4 * m + 1], fmaf(-au.y, us, k.y * vj));
+            s[4 * m + 2] = fmaf(d.z, s[4 * m + 2], fmaf(-au.z, us, k.z * vj));
+            s[4 * m + 3] = fmaf(d.w, s[4 * m + 3], fmaf(-au.w, us, k.w * vj));
+            o0 = fmaf(s[4 * m], q.x, o0);
+            o1 = fmaf(s[4 * m + 1], q.y, o1);
+            o2 = fmaf(s[4 * m + 2], q.z, o2);
+            o3 = fmaf(s[4 * m + 3], q.w, o3);
+          }
+        } else {
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const float4 k = k4[part + P * m], q = q4[part + P * m];
+            s[4 * m] = fmaf(c_h, s[4 * m], k.x * vj);
+            s[4 * m + 1] = fmaf(c_h, s[4 * m + 1], k.y * vj);
+            s[4 * m + 2] = fmaf(c_h, s[4 * m + 2], k.z * vj);
+            s[4 * m + 3] = fmaf(c_h, s[4 * m + 3], k.w * vj);
+            o0 = fmaf(s[4 * m], q.x, o0);
+            o1 = fmaf(s[4 * m + 1], q.y, o1);
+            o2 = fmaf(s[4 * m + 2], q.z, o2);
+            o3 = fmaf(s[4 * m + 3], q.w, o3);
+          }
+        }
+        float o = (o0 + o1) + (o2 + o3);
+        for (int off = P >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+        if (part == 0 && owns) y[(long long)(t0 + t) * H * VD + (long long)h * VD + j] = o;
+      }
+    }
+    __syncthreads();
   }
   if (write_state && owns) {
 #pragma unroll
@@ -190,11 +396,31 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ y, const G* __r
 
 using namespace tl;
 
+// Threads a block (a multiple of 32, at least P) and the value columns it takes: the largest block that still gives the GPU
+// two blocks an SM, else a single warp; never more columns than there are.
+static void recurrence_block(int requests, int H, int VD, int P, int sm_count, int* threads, int* cols) {
+  const int needed = ((VD * P + 31) / 32) * 32;
+  int th = REC_THREADS;
+  while (th > 32 && th / 2 >= P && (long long)requests * H * ceil_div(VD, th / P) < 2LL * sm_count) th >>= 1;
+  if (th > needed) th = needed;
+  if (th < P) th = P;
+  *threads = th;
+  *cols = th / P;
+}
+
+// floats of scratch the staged form wants for `rows` rows: the prepared tokens, then (fixed decays) the activated values
+extern "C" long long tl_recurrence_scratch_floats(long long rows, int H, int D, int VD, int delta) {
+  int P = 1;
+  while (16 * P < D) P <<= 1;
+  return rows * H * ((delta ? 5 : 2) * 16LL * P + (delta ? 0 : VD));
+}
+
+// scratch: null runs the one-kernel form (steps of a few rows a request); else tl_recurrence_scratch_floats(rows, ...) floats.
 extern "C" int tl_recurrence_scan(const float* proj, long long ld, int q_col, int k_col, int v_col, int a_col, const float* wl,
                                   long long ld_w, const float* w0, const float* a_bias, const float* head_decay, float rate,
                                   float key_eps, int silu_inputs, float* state, long long slot_floats, const int* state_slot,
                                   const int* row_start, int requests, float* y, int H, int D, int VD, int write_state,
-                                  cudaStream_t stream) {
+                                  float* scratch, long long rows, int sm_count, cudaStream_t stream) {
   if (requests == 0) return 0;
   const bool delta = wl != nullptr;
   TL_REQUIRE(H > 0 && D >= 1 && D <= 512 && VD >= 1, "recurrence_scan: %d heads, %d keys (up to 512), %d values", H, D, VD);
@@ -203,22 +429,65 @@ extern "C" int tl_recurrence_scan(const float* proj, long long ld, int q_col, in
   TL_REQUIRE(H <= 65535, "recurrence_scan: %d heads exceed the grid limit", H);
   int P = 1;
   while (16 * P < D) P <<= 1;
-  const int cols_per_block = min(REC_THREADS / P, ((VD + 7) / 8) * 8);
+  int threads, cols_per_block;
+  recurrence_block(requests, H, VD, P, sm_count > 0 ? sm_count : 148, &threads, &cols_per_block);
   const int tiles = ceil_div(VD, cols_per_block);
-  const size_t smem = (size_t)((delta ? 5 : 2) * REC_TOKENS * 16 * P + REC_TOKENS * cols_per_block) * sizeof(float);
+  TL_REQUIRE(tiles <= 65535, "recurrence_scan: %d tiles of value columns exceed the grid limit", tiles);
   dim3 grid(requests, H, tiles);
+  const int narr = delta ? 5 : 2, Dp = 16 * P;
+  if (scratch) {
+    const long long pairs = rows * H;
+    float* prep = scratch;
+    float* vact = delta ? nullptr : scratch + pairs * narr * Dp;
+    const unsigned pblocks = (unsigned)((pairs + 3) / 4);
+    if (delta)
+      recurrence_prepare_kernel<true><<<pblocks, 128, 0, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias, rate,
+                                                                   key_eps, silu_inputs, prep, vact, H, D, VD, Dp, pairs);
+    else
+      recurrence_prepare_kernel<false><<<pblocks, 128, 0, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias, rate,
+                                                                    key_eps, silu_inputs, prep, vact, H, D, VD, Dp, pairs);
+    TL_LAUNCH_CHECK();
+    // tokens a stage and stages: as deep a ring as 96 KB hold
+    int TC = 16, stages = 4;
+    auto bytes = [&](int tc, int st) { return (size_t)st * tc * (narr * Dp + cols_per_block) * sizeof(float); };
+    if (bytes(TC, stages) > 96 * 1024) stages = 2;
+    while (TC > 1 && bytes(TC, stages) > 96 * 1024) TC >>= 1;
+    const size_t smem = bytes(TC, stages);
+    const float* vsrc = delta ? proj : vact;
+    const long long ld_v = delta ? ld : (long long)H * VD;
+    const int vc = delta ? v_col : 0;
+#define TL_RSS(DELTA_, ST_)                                                                                                   \
+  do {                                                                                                                        \
+    if (smem > 48 * 1024)                                                                                                     \
+      cudaFuncSetAttribute(recurrence_scan_staged_kernel<DELTA_, ST_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
+    recurrence_scan_staged_kernel<DELTA_, ST_><<<grid, threads + 32, smem, stream>>>(prep, vsrc, ld_v, vc, head_decay, state,         \
+                                                                                slot_floats, state_slot, row_start, y, H, D, VD, \
+                                                                                P, cols_per_block, TC, write_state);             \
+  } while (0)
+    if (delta) {
+      if (stages == 4) TL_RSS(true, 4);
+      else TL_RSS(true, 2);
+    } else {
+      if (stages == 4) TL_RSS(false, 4);
+      else TL_RSS(false, 2);
+    }
+#undef TL_RSS
+    TL_LAUNCH_CHECK();
+    return 0;
+  }
+  const size_t smem = (size_t)(narr * REC_TOKENS * Dp + REC_TOKENS * cols_per_block) * sizeof(float);
   if (delta) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(recurrence_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    recurrence_scan_kernel<true><<<grid, REC_THREADS, smem, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias,
-                                                                      head_decay, rate, key_eps, silu_inputs, state, slot_floats,
-                                                                      state_slot, row_start, y, H, D, VD, P, cols_per_block,
-                                                                      write_state);
+    recurrence_scan_kernel<true><<<grid, threads, smem, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias,
+                                                                  head_decay, rate, key_eps, silu_inputs, state, slot_floats,
+                                                                  state_slot, row_start, y, H, D, VD, P, cols_per_block,
+                                                                  write_state);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(recurrence_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    recurrence_scan_kernel<false><<<grid, REC_THREADS, smem, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias,
-                                                                       head_decay, rate, key_eps, silu_inputs, state, slot_floats,
-                                                                       state_slot, row_start, y, H, D, VD, P, cols_per_block,
-                                                                       write_state);
+    recurrence_scan_kernel<false><<<grid, threads, smem, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias,
+                                                                   head_decay, rate, key_eps, silu_inputs, state, slot_floats,
+                                                                   state_slot, row_start, y, H, D, VD, P, cols_per_block,
+                                                                   write_state);
   }
   TL_LAUNCH_CHECK();
   return 0;

@@ -133,7 +133,8 @@ _SIGNATURES = {
                           c_int, c_int, c_int, c_void_p, c_void_p],
     "tl_recurrence_scan": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                            c_float, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-                           c_int, c_int, c_void_p],
+                           c_int, c_int, c_void_p, c_longlong, c_int, c_void_p],
+    "tl_recurrence_scratch_floats": [c_longlong, c_int, c_int, c_int, c_int],
     "tl_group_norm_gate": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_float, c_float, c_void_p, c_longlong, c_int,
                            c_int, c_int, c_int, c_void_p],
     "tl_set_gate_constants": [c_float, c_float],
@@ -162,6 +163,7 @@ def core():
             fn.restype = c_int
         lib.tl_headmix_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
         lib.tl_headmix_scratch_floats.restype = c_longlong
+        lib.tl_recurrence_scratch_floats.restype = c_longlong
         lib.tl_ssm_scan_scratch.argtypes = [c_int, c_int, c_int, c_int, c_int]
         lib.tl_ssm_scan_scratch.restype = c_longlong
         lib.tl_last_error.restype = ctypes.c_char_p
@@ -722,21 +724,33 @@ def attention_flex(q, k_cache, v_cache, table, page_size: int, req_of_row, posit
     return out
 
 
+RECURRENCE_STAGED_ROWS = 8      # a request that brings more rows than this takes the step to the two-kernel form
+
+
 def recurrence_scan(proj, q_col: int, k_col: int, v_col: int, state, state_slot, row_start, requests: int, y, heads: int,
                     key_dim: int, value_dim: int, *, head_decay=None, a_col: int = -1, w=None, w0=None, a_bias=None,
-                    rate: float = 0.0, key_eps: float = 0.0, silu_inputs: bool = False, write_state: bool = True) -> torch.Tensor:
+                    rate: float = 0.0, key_eps: float = 0.0, silu_inputs: bool = False, write_state: bool = True,
+                    max_rows: int = 1) -> torch.Tensor:
     """The recurrence over a matrix state a head (csrc/recurrence.cu): with `head_decay` (float32 [heads]) the decayed sum of
     outer products, with `w` (float32 [rows, heads * key_dim], the decay's logits) the generalized delta rule. `proj`:
     float32 rows holding q, k, v (and the removal logits at `a_col`) at the given columns; `state` [slots, heads, key_dim,
-    value_dim] float32; `y` [rows, heads * value_dim] float32."""
+    value_dim] float32; `y` [rows, heads * value_dim] float32. `max_rows`: the most rows a request brings; above
+    RECURRENCE_STAGED_ROWS the tokens' activations, decays and unit keys are formed side by side first and the scan fetches
+    them ahead of its loop."""
     _need(proj, torch.float32, "projections"); _need(state, torch.float32, "state"); _need(y, torch.float32, "y")
     if w is not None:
         _need(w, torch.float32, "decay logits")
+    rows = proj.shape[0]
+    scratch = None
+    if max_rows > RECURRENCE_STAGED_ROWS:
+        scratch = torch.empty(core().tl_recurrence_scratch_floats(rows, heads, key_dim, value_dim, int(w is not None)),
+                              dtype=torch.float32, device=proj.device)
     check(core().tl_recurrence_scan(ptr(proj), proj.stride(0), int(q_col), int(k_col), int(v_col), int(a_col), ptr(w),
                                     w.stride(0) if w is not None else 0, ptr(w0), ptr(a_bias), ptr(head_decay), float(rate),
                                     float(key_eps), int(silu_inputs), ptr(state), state[0].numel(), ptr(state_slot),
                                     ptr(row_start), int(requests), ptr(y), heads, key_dim, value_dim, int(write_state),
-                                    stream()), "recurrence_scan")
+                                    ptr(scratch), rows, sm_count(), stream()), "recurrence_scan",
+          kernels=2 if scratch is not None else 1)
     return y
 
 

@@ -85,7 +85,8 @@ class DecayedLinearAttention(Part):
         y = torch.empty(R, self.out_dim, dtype=torch.float32, device=dev)
         ops.recurrence_scan(proj, self.col["q"], self.col["k"], self.col["v"], cache.state, step.state_slot, step.row_start,
                             step.n_requests, y, self.heads, self.head_dim, self.value_dim, head_decay=self.head_decay,
-                            silu_inputs=self.activation == "silu", write_state=writes_cache)
+                            silu_inputs=self.activation == "silu", write_state=writes_cache,
+                            max_rows=step.max_rows_per_request)
         return ops.group_norm_gate(y, proj[:, self.col["gate"]:], proj.stride(0), self.w_norm, self.eps, 1, out_scale, out)
 
     def forward(self, x, step, cache, writes_cache: bool = True):
@@ -156,7 +157,8 @@ class DeltaRuleMixer(Part):
         y = torch.empty(R, self.out_dim, dtype=torch.float32, device=dev)
         ops.recurrence_scan(proj, self.col["r"], self.col["k"], self.col["v"], cache.state, step.state_slot, step.row_start,
                             step.n_requests, y, self.heads, self.head_dim, self.head_dim, a_col=self.col["a"], w=w, w0=self.w0,
-                            a_bias=self.a_bias, rate=self.decay_rate, key_eps=self.key_eps, write_state=writes_cache)
+                            a_bias=self.a_bias, rate=self.decay_rate, key_eps=self.key_eps, write_state=writes_cache,
+                            max_rows=step.max_rows_per_request)
         return ops.group_norm_gate(y, proj[:, self.col["gate"]:], proj.stride(0), self.w_norm, self.eps, self.heads, out_scale,
                                    out)
 
