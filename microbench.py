@@ -240,6 +240,65 @@ def latent(a) -> dict:
             "rot_dim": Rr, "ms": ms, "flops": flops, "TFLOPs": flops / ms / 1e9, "bytes": nbytes, "GBps": nbytes / ms / 1e6}
 
 
+def recurrence(a) -> dict:
+    """The recurrence over a matrix state a head of one layer (`--rule delta` or `decay`): `batch` requests of `rows` rows."""
+    from tandemllm_b200.kernels import ops
+    ops.core()
+    H, D, VD, B, R = a.heads, a.dim, a.vdim, a.batch, a.rows
+    delta = a.rule == "delta"
+    if delta:
+        VD = D
+    I = H * D
+    cols = {"q": 0, "k": I, "v": 2 * I, "a": 2 * I + H * VD}
+    proj = torch.randn(B * R, cols["a"] + I, device=DEV) * 0.5
+    state = torch.zeros(B, H, D, VD, device=DEV)
+    y = torch.empty(B * R, H * VD, device=DEV)
+    slot = torch.arange(B, dtype=torch.int32, device=DEV)
+    start = torch.arange(0, (B + 1) * R, R, dtype=torch.int32, device=DEV)
+    kw = dict(a_col=cols["a"], w=torch.randn(B * R, I, device=DEV), w0=torch.zeros(I, device=DEV), a_bias=torch.zeros(I, device=DEV),
+              rate=0.6, key_eps=1e-6) if delta else dict(head_decay=torch.full((H,), 0.97, device=DEV), silu_inputs=True)
+    ms = timed(lambda: ops.recurrence_scan(proj, cols["q"], cols["k"], cols["v"], state, slot, start, B, y, H, D, VD,
+                                           max_rows=R, **kw), a.iters)
+    flops = (10.0 if delta else 6.0) * B * R * H * D * VD
+    nbytes = 4.0 * (proj.numel() + y.numel() + 2 * state.numel())
+    return {"kernel": f"matrix-state recurrence ({a.rule})", "batch": B, "rows": R, "heads": H, "dim": D, "vdim": VD, "ms": ms,
+            "flops": flops, "TFLOPs_fp32": flops / ms / 1e9, "bytes": nbytes, "GBps": nbytes / ms / 1e6,
+            "ns_per_token_of_a_request": ms * 1e6 / R}
+
+
+def flex(a) -> dict:
+    """Attention with capped scores, a window that keeps first tokens, a turned output and optionally a gate, on the tensor
+    cores: `batch` requests of `rows` rows at a context of `context`."""
+    from tandemllm_b200.parts import PagedSiteCache, StepContext
+    rt = runtime()
+    Hq, Hk, D, VD, B, R, ctx, win, page = a.heads, a.kv_heads, a.dim, a.vdim, a.batch, a.rows, a.context, a.window, 16
+    pages_each = -(-ctx // page)
+    k = (torch.randn(B * pages_each, Hk, page, D, device=DEV) * 0.5).to(torch.bfloat16)
+    v = (torch.randn(B * pages_each, Hk, page, VD, device=DEV) * 0.5).to(torch.bfloat16)
+    cache = PagedSiteCache(0, page, k, v)
+    table = torch.arange(B * pages_each, dtype=torch.int32, device=DEV).view(B, pages_each)
+    q = (torch.randn(B * R, Hq, D, device=DEV)).to(torch.bfloat16)
+    out = torch.empty(B * R, Hq * VD, dtype=torch.bfloat16, device=DEV)
+    pos = torch.cat([torch.arange(ctx - R, ctx, dtype=torch.int32) for _ in range(B)]).to(DEV)
+    req = torch.arange(B, dtype=torch.int32).repeat_interleave(R).to(DEV)
+    starts = list(range(0, (B + 1) * R, R))
+    step = StepContext(n_rows=B * R, n_requests=B, token_ids=None, positions=pos, req_of_row=req,
+                       row_start=torch.tensor(starts, dtype=torch.int32, device=DEV), state_slot=None, block_tables=[table],
+                       out_rows=None, n_out=0, max_rows_per_request=R, max_context=ctx, host={"row_start": starts})
+    inv = (10000.0 ** (-torch.arange(0, VD, 2, dtype=torch.float64) / VD)).float().to(DEV) if a.turned else None
+    part = types.SimpleNamespace(scale=D ** -0.5, softcap=a.softcap or None, window=win or None, keep_first=a.keep_first,
+                                 inv_freq_v=inv)
+    assert rt.tensorcore.attention_flex(part, q, cache, table, step, None, 0, 1.0, out), "sizes the kernel does not take"
+    ms = timed(lambda: rt.tensorcore.attention_flex(part, q, cache, table, step, None, 0, 1.0, out), a.iters)
+    seen = lambda p: (min(p + 1, win) + min(a.keep_first, max(0, p + 1 - win))) if win else p + 1
+    pairs = B * sum(seen(p) for p in range(ctx - R, ctx))
+    flops = pairs * Hq * 2.0 * (D + VD)
+    nbytes = 2.0 * B * Hk * min(ctx, (win + a.keep_first + R) if win else ctx) * (D + VD) + q.numel() * 2 + out.numel() * 2
+    return {"kernel": "attention, capped scores and kept first tokens (mma.sync)", "batch": B, "rows": R, "context": ctx,
+            "window": win, "keep_first": a.keep_first, "heads": Hq, "kv_heads": Hk, "dim": D, "vdim": VD, "ms": ms, "flops": flops,
+            "TFLOPs": flops / ms / 1e9, "bytes": nbytes, "GBps": nbytes / ms / 1e6}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -290,17 +349,36 @@ def main(argv=None) -> int:
     la.add_argument("--heads", type=int, default=16)
     la.add_argument("--kv-rank", type=int, default=256)
     la.add_argument("--rot-dim", type=int, default=32)
+    rc = sub.add_parser("recurrence")
+    rc.add_argument("--rule", default="delta", choices=("delta", "decay"))
+    rc.add_argument("--batch", type=int, default=1)
+    rc.add_argument("--rows", type=int, default=2048)
+    rc.add_argument("--heads", type=int, default=16)
+    rc.add_argument("--dim", type=int, default=64)
+    rc.add_argument("--vdim", type=int, default=64)
+    fl = sub.add_parser("flex")
+    fl.add_argument("--batch", type=int, default=1)
+    fl.add_argument("--rows", type=int, default=2048)
+    fl.add_argument("--context", type=int, default=2048)
+    fl.add_argument("--window", type=int, default=512)
+    fl.add_argument("--keep-first", type=int, default=4)
+    fl.add_argument("--softcap", type=float, default=50.0)
+    fl.add_argument("--turned", type=int, default=1)
+    fl.add_argument("--heads", type=int, default=16)
+    fl.add_argument("--kv-heads", type=int, default=4)
+    fl.add_argument("--dim", type=int, default=64)
+    fl.add_argument("--vdim", type=int, default=64)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=8)
     n.add_argument("--hidden", type=int, default=2048)
     for p in (e, d):
         p.add_argument("--product", default="pair", choices=("pair", "single"),
                        help="prompt-sized products: the kernel on pairs of SMs (cta_group::2), or the one-CTA persistent kernel")
-    for p in (e, d, t, n, hm, sc, la):
+    for p in (e, d, t, n, hm, sc, la, rc, fl):
         p.add_argument("--iters", type=int, default=20)
     a = ap.parse_args(argv)
     result = {"expert_gemm": expert_gemm, "dense_gemm": dense_gemm, "attention": attention, "norm": norm, "headmix": headmix,
-              "scan": scan, "latent": latent}[a.what](a)
+              "scan": scan, "latent": latent, "recurrence": recurrence, "flex": flex}[a.what](a)
     print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in result.items()}))
     return 0
 

@@ -244,14 +244,20 @@ __device__ __forceinline__ void rec_cp4(float* dst, const float* src) {
 // producer, which does nothing but fetch: it keeps STAGES - 1 chunks of TC tokens in flight (each token's NARR * Dp prepared
 // floats, then the chunk's TC * cols_per_block values) and meets the computing warps at one barrier a chunk, when the next
 // chunk has landed and the last one has been read.
-template <bool DELTA, int STAGES>
+// KPL keys of a column a lane (16 or 4): with 4, four times as many lanes share a column and a token takes a warp a
+// third of the instructions, at the price of two more lane crossings a sum; the launcher takes 4 where the GPU would
+// otherwise stand idle. DP: the keys a head, filled up to a power of two (16 at least); sizes known to the compiler keep
+// the loop free of address arithmetic.
+constexpr int REC_STAGES = 3;
+template <bool DELTA, int KPL, int DP>
 __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kernel(
     const float* __restrict__ prep, const float* __restrict__ vsrc, long long ld_v, int v_col, const float* __restrict__ head_decay,
     float* __restrict__ state, long long slot_floats, const int* __restrict__ state_slot, const int* __restrict__ row_start,
-    float* __restrict__ y, int H, int D, int VD, int P, int cols_per_block, int TC, int write_state) {
+    float* __restrict__ y, int H, int D, int VD, int cols_per_block, int TC, int write_state) {
+  constexpr int STAGES = REC_STAGES, P = DP / KPL, Dp = DP;
   extern __shared__ __align__(16) float sm[];
   constexpr int NARR = DELTA ? 5 : 2;
-  const int Dp = 16 * P, tok_floats = NARR * Dp;
+  constexpr int M = KPL / 4, tok_floats = NARR * Dp;
   const int stage_floats = TC * (tok_floats + cols_per_block);
   const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols_per_block;
   const int tid = threadIdx.x, nth = blockDim.x - 32;
@@ -280,7 +286,7 @@ __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kerne
       }
     }
   };
-  float s[16];
+  float s[KPL];
   if (producer) {
 #pragma unroll
     for (int s0 = 0; s0 < STAGES - 1; ++s0) {
@@ -290,7 +296,7 @@ __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kerne
     asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");       // chunk 0 has landed
   } else {
 #pragma unroll
-    for (int m = 0; m < 4; ++m)
+    for (int m = 0; m < M; ++m)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int i = 4 * (part + P * m) + c;
@@ -309,63 +315,111 @@ __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kerne
       const int t0 = r0 + chunk * TC, nt = min(TC, r1 - t0);
       const float* base = sm + (chunk % STAGES) * stage_floats;
       const float* vb = base + TC * tok_floats;
-      for (int t = 0; t < nt; ++t) {
-        const float4* q4 = reinterpret_cast<const float4*>(base + t * tok_floats);
-        const float4* k4 = q4 + Dp / 4;
-        const float vj = vb[t * cols_per_block + jl];
-        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-        if (DELTA) {
-          const float4* d4 = k4 + Dp / 4;
-          const float4* u4 = d4 + Dp / 4;
-          const float4* au4 = u4 + Dp / 4;
-          // four short chains of additions instead of one long one: the sum over keys is what the next token waits for
-          float us0 = 0.f, us1 = 0.f, us2 = 0.f, us3 = 0.f;
+      float* yo = y + (long long)t0 * H * VD + (long long)h * VD + j;
+      const long long ldy = (long long)H * VD;
+      // The loop is arranged by hand so that no load's latency lies on the state's chain: what a token needs first is
+      // fetched while the token before is computed, the rest while the sum over keys crosses the lanes; the output of a
+      // token crosses the lanes together with the next token's sum over keys.
+      float o_pend = 0.f;
+      if (DELTA) {
+        float4 u[M];
 #pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            const float4 u = u4[part + P * m];
-            us0 = fmaf(u.x, s[4 * m], us0);
-            us1 = fmaf(u.y, s[4 * m + 1], us1);
-            us2 = fmaf(u.z, s[4 * m + 2], us2);
-            us3 = fmaf(u.w, s[4 * m + 3], us3);
+        for (int m = 0; m < M; ++m) u[m] = reinterpret_cast<const float4*>(base + 3 * Dp)[part + P * m];
+#pragma unroll 2
+        for (int t = 0; t < nt; ++t) {
+          const float4* q4 = reinterpret_cast<const float4*>(base + t * tok_floats);
+          const float4* k4 = q4 + Dp / 4;
+          const float4* d4 = k4 + Dp / 4;
+          const float4* au4 = d4 + 2 * (Dp / 4);
+          float4 d[M], au[M], k[M], q[M];
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            d[m] = d4[part + P * m];
+            au[m] = au4[part + P * m];
+            k[m] = k4[part + P * m];
+            q[m] = q4[part + P * m];
+          }
+          const float vj = vb[t * cols_per_block + jl];
+          float us0 = 0.f, us1 = 0.f, us2 = 0.f, us3 = 0.f;      // four short chains of additions instead of one long one
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            us0 = fmaf(u[m].x, s[4 * m], us0);
+            us1 = fmaf(u[m].y, s[4 * m + 1], us1);
+            us2 = fmaf(u[m].z, s[4 * m + 2], us2);
+            us3 = fmaf(u[m].w, s[4 * m + 3], us3);
           }
           float us = (us0 + us1) + (us2 + us3);
-          for (int off = P >> 1; off > 0; off >>= 1) us += __shfl_xor_sync(0xffffffffu, us, off);
+          if (t + 1 < nt) {
+            const float4* un = reinterpret_cast<const float4*>(base + (t + 1) * tok_floats + 3 * Dp);
 #pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            const float4 d = d4[part + P * m], au = au4[part + P * m], k = k4[part + P * m], q = q4[part + P * m];
-            s[4 * m] = fmaf(d.x, s[4 * m], fmaf(-au.x, us, k.x * vj));
-            s[4 * m + 1] = fmaf(d.y, s[4 * m + 1], fmaf(-au.y, us, k.y * vj));
-            s[4 * m + 2] = fmaf(d.z, s[4 * m + 2], fmaf(-au.z, us, k.z * vj));
-            s[4 * m + 3] = fmaf(d.w, s[4 * m + 3], fmaf(-au.w, us, k.w * vj));
-            o0 = fmaf(s[4 * m], q.x, o0);
-            o1 = fmaf(s[4 * m + 1], q.y, o1);
-            o2 = fmaf(s[4 * m + 2], q.z, o2);
-            o3 = fmaf(s[4 * m + 3], q.w, o3);
+            for (int m = 0; m < M; ++m) u[m] = un[part + P * m];
           }
-        } else {
+          #pragma unroll
+          for (int off = P >> 1; off > 0; off >>= 1) {
+            us += __shfl_xor_sync(0xffffffffu, us, off);
+            o_pend += __shfl_xor_sync(0xffffffffu, o_pend, off);
+          }
+          if (t > 0 && part == 0 && owns) yo[(t - 1) * ldy] = o_pend;
+          float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            const float4 k = k4[part + P * m], q = q4[part + P * m];
-            s[4 * m] = fmaf(c_h, s[4 * m], k.x * vj);
-            s[4 * m + 1] = fmaf(c_h, s[4 * m + 1], k.y * vj);
-            s[4 * m + 2] = fmaf(c_h, s[4 * m + 2], k.z * vj);
-            s[4 * m + 3] = fmaf(c_h, s[4 * m + 3], k.w * vj);
-            o0 = fmaf(s[4 * m], q.x, o0);
-            o1 = fmaf(s[4 * m + 1], q.y, o1);
-            o2 = fmaf(s[4 * m + 2], q.z, o2);
-            o3 = fmaf(s[4 * m + 3], q.w, o3);
+          for (int m = 0; m < M; ++m) {
+            s[4 * m] = fmaf(d[m].x, s[4 * m], fmaf(-au[m].x, us, k[m].x * vj));
+            s[4 * m + 1] = fmaf(d[m].y, s[4 * m + 1], fmaf(-au[m].y, us, k[m].y * vj));
+            s[4 * m + 2] = fmaf(d[m].z, s[4 * m + 2], fmaf(-au[m].z, us, k[m].z * vj));
+            s[4 * m + 3] = fmaf(d[m].w, s[4 * m + 3], fmaf(-au[m].w, us, k[m].w * vj));
+            o0 = fmaf(s[4 * m], q[m].x, o0);
+            o1 = fmaf(s[4 * m + 1], q[m].y, o1);
+            o2 = fmaf(s[4 * m + 2], q[m].z, o2);
+            o3 = fmaf(s[4 * m + 3], q[m].w, o3);
           }
+          o_pend = (o0 + o1) + (o2 + o3);
         }
-        float o = (o0 + o1) + (o2 + o3);
-        for (int off = P >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-        if (part == 0 && owns) y[(long long)(t0 + t) * H * VD + (long long)h * VD + j] = o;
+      } else {
+        float4 k[M], q[M];
+        float vj = vb[jl];
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          k[m] = reinterpret_cast<const float4*>(base + Dp)[part + P * m];
+          q[m] = reinterpret_cast<const float4*>(base)[part + P * m];
+        }
+#pragma unroll 2
+        for (int t = 0; t < nt; ++t) {
+          float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            s[4 * m] = fmaf(c_h, s[4 * m], k[m].x * vj);
+            s[4 * m + 1] = fmaf(c_h, s[4 * m + 1], k[m].y * vj);
+            s[4 * m + 2] = fmaf(c_h, s[4 * m + 2], k[m].z * vj);
+            s[4 * m + 3] = fmaf(c_h, s[4 * m + 3], k[m].w * vj);
+            o0 = fmaf(s[4 * m], q[m].x, o0);
+            o1 = fmaf(s[4 * m + 1], q[m].y, o1);
+            o2 = fmaf(s[4 * m + 2], q[m].z, o2);
+            o3 = fmaf(s[4 * m + 3], q[m].w, o3);
+          }
+          if (t + 1 < nt) {
+            const float4* qn = reinterpret_cast<const float4*>(base + (t + 1) * tok_floats);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+              q[m] = qn[part + P * m];
+              k[m] = qn[Dp / 4 + part + P * m];
+            }
+            vj = vb[(t + 1) * cols_per_block + jl];
+          }
+          #pragma unroll
+          for (int off = P >> 1; off > 0; off >>= 1) o_pend += __shfl_xor_sync(0xffffffffu, o_pend, off);
+          if (t > 0 && part == 0 && owns) yo[(t - 1) * ldy] = o_pend;
+          o_pend = (o0 + o1) + (o2 + o3);
+        }
       }
+      #pragma unroll
+          for (int off = P >> 1; off > 0; off >>= 1) o_pend += __shfl_xor_sync(0xffffffffu, o_pend, off);
+      if (part == 0 && owns) yo[(nt - 1) * ldy] = o_pend;
     }
     __syncthreads();
   }
   if (write_state && owns) {
 #pragma unroll
-    for (int m = 0; m < 4; ++m)
+    for (int m = 0; m < M; ++m)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int i = 4 * (part + P * m) + c;
@@ -397,11 +451,13 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ y, const G* __r
 using namespace tl;
 
 // Threads a block (a multiple of 32, at least P) and the value columns it takes: the largest block that still gives the GPU
-// two blocks an SM, else a single warp; never more columns than there are.
-static void recurrence_block(int requests, int H, int VD, int P, int sm_count, int* threads, int* cols) {
+// `want_blocks` blocks, else a single warp; never more columns than there are. (Steps of a few rows want many blocks in
+// flight for the states they read and write; the staged form's blocks each fetch every prepared token of their head, so
+// they stay as large as fills three SMs in four.)
+static void recurrence_block(int requests, int H, int VD, int P, long long want_blocks, int* threads, int* cols) {
   const int needed = ((VD * P + 31) / 32) * 32;
   int th = REC_THREADS;
-  while (th > 32 && th / 2 >= P && (long long)requests * H * ceil_div(VD, th / P) < 2LL * sm_count) th >>= 1;
+  while (th > 32 && th / 2 >= P && (long long)requests * H * ceil_div(VD, th / P) < want_blocks) th >>= 1;
   if (th > needed) th = needed;
   if (th < P) th = P;
   *threads = th;
@@ -429,12 +485,20 @@ extern "C" int tl_recurrence_scan(const float* proj, long long ld, int q_col, in
   TL_REQUIRE(H <= 65535, "recurrence_scan: %d heads exceed the grid limit", H);
   int P = 1;
   while (16 * P < D) P <<= 1;
+  const int P16 = P;
+  const int sms = sm_count > 0 ? sm_count : 148;
+  // the staged form gives a column to four times as many lanes (4 keys a lane) until the GPU has two warps a scheduler
+  int kpl = 16;
+  if (scratch && 4 * P <= 32 && (long long)requests * H * VD * P < 256LL * sms) {
+    kpl = 4;
+    P *= 4;
+  }
   int threads, cols_per_block;
-  recurrence_block(requests, H, VD, P, sm_count > 0 ? sm_count : 148, &threads, &cols_per_block);
+  recurrence_block(requests, H, VD, P, scratch ? (3LL * sms) / 4 : 2LL * sms, &threads, &cols_per_block);
   const int tiles = ceil_div(VD, cols_per_block);
   TL_REQUIRE(tiles <= 65535, "recurrence_scan: %d tiles of value columns exceed the grid limit", tiles);
   dim3 grid(requests, H, tiles);
-  const int narr = delta ? 5 : 2, Dp = 16 * P;
+  const int narr = delta ? 5 : 2, Dp = 16 * P16;
   if (scratch) {
     const long long pairs = rows * H;
     float* prep = scratch;
@@ -447,30 +511,43 @@ extern "C" int tl_recurrence_scan(const float* proj, long long ld, int q_col, in
       recurrence_prepare_kernel<false><<<pblocks, 128, 0, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias, rate,
                                                                     key_eps, silu_inputs, prep, vact, H, D, VD, Dp, pairs);
     TL_LAUNCH_CHECK();
-    // tokens a stage and stages: as deep a ring as 96 KB hold
-    int TC = 16, stages = 4;
-    auto bytes = [&](int tc, int st) { return (size_t)st * tc * (narr * Dp + cols_per_block) * sizeof(float); };
-    if (bytes(TC, stages) > 96 * 1024) stages = 2;
-    while (TC > 1 && bytes(TC, stages) > 96 * 1024) TC >>= 1;
-    const size_t smem = bytes(TC, stages);
+    // tokens a stage: as many (16 at most) as 96 KB hold in three stages
+    int TC = 16;
+    auto bytes = [&](int tc) { return (size_t)REC_STAGES * tc * (narr * Dp + cols_per_block) * sizeof(float); };
+    while (TC > 1 && bytes(TC) > 96 * 1024) TC >>= 1;
+    const size_t smem = bytes(TC);
     const float* vsrc = delta ? proj : vact;
     const long long ld_v = delta ? ld : (long long)H * VD;
     const int vc = delta ? v_col : 0;
-#define TL_RSS(DELTA_, ST_)                                                                                                   \
-  do {                                                                                                                        \
-    if (smem > 48 * 1024)                                                                                                     \
-      cudaFuncSetAttribute(recurrence_scan_staged_kernel<DELTA_, ST_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
-    recurrence_scan_staged_kernel<DELTA_, ST_><<<grid, threads + 32, smem, stream>>>(prep, vsrc, ld_v, vc, head_decay, state,         \
-                                                                                slot_floats, state_slot, row_start, y, H, D, VD, \
-                                                                                P, cols_per_block, TC, write_state);             \
+#define TL_RSS(DELTA_, KPL_, DP_)                                                                                               \
+  do {                                                                                                                          \
+    if (smem > 48 * 1024)                                                                                                       \
+      cudaFuncSetAttribute(recurrence_scan_staged_kernel<DELTA_, KPL_, DP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+                           96 * 1024);                                                                                          \
+    recurrence_scan_staged_kernel<DELTA_, KPL_, DP_><<<grid, threads + 32, smem, stream>>>(                                     \
+        prep, vsrc, ld_v, vc, head_decay, state, slot_floats, state_slot, row_start, y, H, D, VD, cols_per_block, TC,           \
+        write_state);                                                                                                           \
   } while (0)
-    if (delta) {
-      if (stages == 4) TL_RSS(true, 4);
-      else TL_RSS(true, 2);
-    } else {
-      if (stages == 4) TL_RSS(false, 4);
-      else TL_RSS(false, 2);
-    }
+#define TL_RSS_D(DELTA_, DP_)                   \
+  do {                                          \
+    if (kpl == 16) TL_RSS(DELTA_, 16, DP_);     \
+    else if (DP_ <= 128) TL_RSS(DELTA_, 4, (DP_ <= 128 ? DP_ : 128)); \
+  } while (0)
+#define TL_RSS_ALL(DELTA_)                      \
+  do {                                          \
+    switch (Dp) {                               \
+      case 16: TL_RSS_D(DELTA_, 16); break;     \
+      case 32: TL_RSS_D(DELTA_, 32); break;     \
+      case 64: TL_RSS_D(DELTA_, 64); break;     \
+      case 128: TL_RSS_D(DELTA_, 128); break;   \
+      case 256: TL_RSS_D(DELTA_, 256); break;   \
+      default: TL_RSS_D(DELTA_, 512); break;    \
+    }                                           \
+  } while (0)
+    if (delta) TL_RSS_ALL(true);
+    else TL_RSS_ALL(false);
+#undef TL_RSS_ALL
+#undef TL_RSS_D
 #undef TL_RSS
     TL_LAUNCH_CHECK();
     return 0;
