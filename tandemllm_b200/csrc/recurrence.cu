@@ -180,8 +180,8 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
   }
 }
 
-// One warp a (row, head): what the scan needs of a token, [rows][H][NARR][Dp] = q, k (activated), and for the delta rule
-// d, u, a * u; entries past D are zero. With `vact`, the activated values [rows][H * VD] as well.
+// One warp a (row, head): what the scan needs of a token, [H][rows][NARR][Dp] = q, k (activated), and for the delta rule
+// d, u, a * u; entries past D are zero (a head's tokens lie together, so a chunk of them is one stretch of memory). With `vact`, the activated values [rows][H * VD] as well.
 template <bool DELTA>
 __global__ void __launch_bounds__(128) recurrence_prepare_kernel(
     const float* __restrict__ proj, long long ld, int q_col, int k_col, int v_col, int a_col, const float* __restrict__ wl,
@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(128) recurrence_prepare_kernel(
   const long long r = idx / H;
   const int h = (int)(idx - r * H);
   const float* row = proj + r * ld + (long long)h * D;
-  float* tq = prep + idx * NARR * Dp;
+  float* tq = prep + ((long long)h * (pairs / H) + r) * NARR * Dp;
   float* tk = tq + Dp;
   float ss = 0.f;
   for (int i = lane; i < Dp; i += 32) {
@@ -240,9 +240,109 @@ __device__ __forceinline__ void rec_cp4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
+// Sums v[0..T) over the P neighbouring lanes that share a column (`part` = the lane's place among them; P divides 32). Each
+// crossing halves what a lane still holds: afterwards v[i], i < T / P, of lane `part` are the whole sums of tokens
+// part * (T / P) + i; with more lanes than tokens, v[0] of the P / T lanes from part = token * (P / T) on is that token's sum.
+constexpr int REC_GROUP = 8;
+constexpr int REC_CHUNK = 16;     // the most tokens a stage holds; a column's values of a stage lie this far apart
+template <int T, int P>
+__device__ __forceinline__ void rec_reduce_scatter(float (&v)[T], int part) {
+#pragma unroll
+  for (int step = 0; (P >> 1 >> step) > 0; ++step) {
+    const int off = P >> 1 >> step;
+    const int cnt = (T >> step) > 1 ? (T >> step) : 1;
+    if (cnt > 1) {
+      const int half = cnt / 2;
+      const bool up = (part & off) != 0;
+#pragma unroll
+      for (int i = 0; i < half; ++i) {
+        const float send = up ? v[i] : v[i + half];
+        const float keep = up ? v[i + half] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    } else {
+      v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+    }
+  }
+}
+
+// REC_GROUP tokens (FULL) or the first n of them for one lane: the lane's KPL keys of its column go through the tokens, the
+// outputs wait in registers and cross the lanes together. Everything a token needs lies at offsets the compiler knows
+// (`tok`: the lane's first four floats of the group's first prepared token; `vcol`: the column's values, a token a float),
+// so the group is straight-line code whose loads the compiler moves ahead of the chain.
+template <bool DELTA, int KPL, int DP, bool FULL>
+__device__ __forceinline__ void rec_group(float (&s)[KPL], const float* __restrict__ tok, const float* __restrict__ vcol,
+                                          float* __restrict__ yg, long long ldy, int n, int part, bool owns, float c_h) {
+  constexpr int P = DP / KPL, M = KPL / 4, tok_floats = (DELTA ? 5 : 2) * DP, Q = DP / 4;
+  float o[REC_GROUP];
+#pragma unroll
+  for (int tt = 0; tt < REC_GROUP; ++tt) {
+    o[tt] = 0.f;
+    if (FULL || tt < n) {
+      const float4* a = reinterpret_cast<const float4*>(tok + tt * tok_floats);
+      const float vj = vcol[tt];
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      if (DELTA) {
+        float us0 = 0.f, us1 = 0.f, us2 = 0.f, us3 = 0.f;      // four short chains of additions instead of one long one
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const float4 u = a[3 * Q + P * m];
+          us0 = fmaf(u.x, s[4 * m], us0);
+          us1 = fmaf(u.y, s[4 * m + 1], us1);
+          us2 = fmaf(u.z, s[4 * m + 2], us2);
+          us3 = fmaf(u.w, s[4 * m + 3], us3);
+        }
+        float us = (us0 + us1) + (us2 + us3);
+#pragma unroll
+        for (int off = P >> 1; off > 0; off >>= 1) us += __shfl_xor_sync(0xffffffffu, us, off);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const float4 q = a[P * m], k = a[Q + P * m], d = a[2 * Q + P * m], au = a[4 * Q + P * m];
+          s[4 * m] = fmaf(d.x, s[4 * m], fmaf(-au.x, us, k.x * vj));
+          s[4 * m + 1] = fmaf(d.y, s[4 * m + 1], fmaf(-au.y, us, k.y * vj));
+          s[4 * m + 2] = fmaf(d.z, s[4 * m + 2], fmaf(-au.z, us, k.z * vj));
+          s[4 * m + 3] = fmaf(d.w, s[4 * m + 3], fmaf(-au.w, us, k.w * vj));
+          o0 = fmaf(s[4 * m], q.x, o0);
+          o1 = fmaf(s[4 * m + 1], q.y, o1);
+          o2 = fmaf(s[4 * m + 2], q.z, o2);
+          o3 = fmaf(s[4 * m + 3], q.w, o3);
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const float4 q = a[P * m], k = a[Q + P * m];
+          s[4 * m] = fmaf(c_h, s[4 * m], k.x * vj);
+          s[4 * m + 1] = fmaf(c_h, s[4 * m + 1], k.y * vj);
+          s[4 * m + 2] = fmaf(c_h, s[4 * m + 2], k.z * vj);
+          s[4 * m + 3] = fmaf(c_h, s[4 * m + 3], k.w * vj);
+          o0 = fmaf(s[4 * m], q.x, o0);
+          o1 = fmaf(s[4 * m + 1], q.y, o1);
+          o2 = fmaf(s[4 * m + 2], q.z, o2);
+          o3 = fmaf(s[4 * m + 3], q.w, o3);
+        }
+      }
+      o[tt] = (o0 + o1) + (o2 + o3);
+    }
+  }
+  rec_reduce_scatter<REC_GROUP, P>(o, part);
+  if (!owns) return;
+  if (P <= REC_GROUP) {
+    constexpr int each = P <= REC_GROUP ? REC_GROUP / P : 1;
+#pragma unroll
+    for (int i = 0; i < each; ++i) {
+      const int t = part * each + i;
+      if (FULL || t < n) yg[t * ldy] = o[i];
+    }
+  } else {
+    constexpr int share = P > REC_GROUP ? P / REC_GROUP : 1;
+    const int t = part / share;
+    if (part % share == 0 && (FULL || t < n)) yg[t * ldy] = o[0];
+  }
+}
+
 // The scan over prepared tokens. Block: cols_per_block * P computing threads (a multiple of 32) and one more warp, the
 // producer, which does nothing but fetch: it keeps STAGES - 1 chunks of TC tokens in flight (each token's NARR * Dp prepared
-// floats, then the chunk's TC * cols_per_block values) and meets the computing warps at one barrier a chunk, when the next
+// floats, then the chunk's values, a column's REC_CHUNK apart) and meets the computing warps at one barrier a chunk, when the next
 // chunk has landed and the last one has been read.
 // KPL keys of a column a lane (16 or 4): with 4, four times as many lanes share a column and a token takes a warp a
 // third of the instructions, at the price of two more lane crossings a sum; the launcher takes 4 where the GPU would
@@ -253,12 +353,12 @@ template <bool DELTA, int KPL, int DP>
 __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kernel(
     const float* __restrict__ prep, const float* __restrict__ vsrc, long long ld_v, int v_col, const float* __restrict__ head_decay,
     float* __restrict__ state, long long slot_floats, const int* __restrict__ state_slot, const int* __restrict__ row_start,
-    float* __restrict__ y, int H, int D, int VD, int cols_per_block, int TC, int write_state) {
+    float* __restrict__ y, long long rows, int H, int D, int VD, int cols_per_block, int TC, int write_state) {
   constexpr int STAGES = REC_STAGES, P = DP / KPL, Dp = DP;
   extern __shared__ __align__(16) float sm[];
   constexpr int NARR = DELTA ? 5 : 2;
   constexpr int M = KPL / 4, tok_floats = NARR * Dp;
-  const int stage_floats = TC * (tok_floats + cols_per_block);
+  const int stage_floats = TC * tok_floats + REC_CHUNK * cols_per_block;
   const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols_per_block;
   const int tid = threadIdx.x, nth = blockDim.x - 32;
   const bool producer = tid >= nth;
@@ -275,15 +375,16 @@ __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kerne
     const int lane = tid - nth;
     const int t0 = r0 + chunk * TC, nt = min(TC, r1 - t0);
     float* base = sm + (chunk % STAGES) * stage_floats;
-    for (int t = 0; t < nt; ++t) {
-      const float* src = prep + ((long long)(t0 + t) * H + h) * tok_floats;
-      for (int p = 4 * lane; p < tok_floats; p += 128) rec_cp16(base + t * tok_floats + p, src + p);
-      float* vb = base + TC * tok_floats + t * cols_per_block;
-      const float* vs = vsrc + (long long)(t0 + t) * ld_v + v_col + (long long)h * VD + col0;
-      for (int c = lane; c < cols_per_block; c += 32) {
-        if (col0 + c < VD) rec_cp4(vb + c, vs + c);
-        else vb[c] = 0.f;
-      }
+    const float* src = prep + ((long long)h * rows + t0) * tok_floats;
+    const int pieces = nt * (tok_floats / 4);
+#pragma unroll 4
+    for (int i = lane; i < pieces; i += 32) rec_cp16(base + 4 * i, src + 4 * i);
+    float* vb = base + TC * tok_floats;
+    const float* vs = vsrc + (long long)t0 * ld_v + v_col + (long long)h * VD + col0;
+    for (int e = lane; e < nt * cols_per_block; e += 32) {
+      const int t = e / cols_per_block, c = e - t * cols_per_block;
+      if (col0 + c < VD) rec_cp4(vb + c * REC_CHUNK + t, vs + (long long)t * ld_v + c);
+      else vb[c * REC_CHUNK + t] = 0.f;
     }
   };
   float s[KPL];
@@ -314,106 +415,14 @@ __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kerne
     } else {
       const int t0 = r0 + chunk * TC, nt = min(TC, r1 - t0);
       const float* base = sm + (chunk % STAGES) * stage_floats;
-      const float* vb = base + TC * tok_floats;
-      float* yo = y + (long long)t0 * H * VD + (long long)h * VD + j;
+      const float* tok = base + 4 * part;
+      const float* vcol = base + TC * tok_floats + jl * REC_CHUNK;
       const long long ldy = (long long)H * VD;
-      // The loop is arranged by hand so that no load's latency lies on the state's chain: what a token needs first is
-      // fetched while the token before is computed, the rest while the sum over keys crosses the lanes; the output of a
-      // token crosses the lanes together with the next token's sum over keys.
-      float o_pend = 0.f;
-      if (DELTA) {
-        float4 u[M];
-#pragma unroll
-        for (int m = 0; m < M; ++m) u[m] = reinterpret_cast<const float4*>(base + 3 * Dp)[part + P * m];
-#pragma unroll 2
-        for (int t = 0; t < nt; ++t) {
-          const float4* q4 = reinterpret_cast<const float4*>(base + t * tok_floats);
-          const float4* k4 = q4 + Dp / 4;
-          const float4* d4 = k4 + Dp / 4;
-          const float4* au4 = d4 + 2 * (Dp / 4);
-          float4 d[M], au[M], k[M], q[M];
-#pragma unroll
-          for (int m = 0; m < M; ++m) {
-            d[m] = d4[part + P * m];
-            au[m] = au4[part + P * m];
-            k[m] = k4[part + P * m];
-            q[m] = q4[part + P * m];
-          }
-          const float vj = vb[t * cols_per_block + jl];
-          float us0 = 0.f, us1 = 0.f, us2 = 0.f, us3 = 0.f;      // four short chains of additions instead of one long one
-#pragma unroll
-          for (int m = 0; m < M; ++m) {
-            us0 = fmaf(u[m].x, s[4 * m], us0);
-            us1 = fmaf(u[m].y, s[4 * m + 1], us1);
-            us2 = fmaf(u[m].z, s[4 * m + 2], us2);
-            us3 = fmaf(u[m].w, s[4 * m + 3], us3);
-          }
-          float us = (us0 + us1) + (us2 + us3);
-          if (t + 1 < nt) {
-            const float4* un = reinterpret_cast<const float4*>(base + (t + 1) * tok_floats + 3 * Dp);
-#pragma unroll
-            for (int m = 0; m < M; ++m) u[m] = un[part + P * m];
-          }
-          #pragma unroll
-          for (int off = P >> 1; off > 0; off >>= 1) {
-            us += __shfl_xor_sync(0xffffffffu, us, off);
-            o_pend += __shfl_xor_sync(0xffffffffu, o_pend, off);
-          }
-          if (t > 0 && part == 0 && owns) yo[(t - 1) * ldy] = o_pend;
-          float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll
-          for (int m = 0; m < M; ++m) {
-            s[4 * m] = fmaf(d[m].x, s[4 * m], fmaf(-au[m].x, us, k[m].x * vj));
-            s[4 * m + 1] = fmaf(d[m].y, s[4 * m + 1], fmaf(-au[m].y, us, k[m].y * vj));
-            s[4 * m + 2] = fmaf(d[m].z, s[4 * m + 2], fmaf(-au[m].z, us, k[m].z * vj));
-            s[4 * m + 3] = fmaf(d[m].w, s[4 * m + 3], fmaf(-au[m].w, us, k[m].w * vj));
-            o0 = fmaf(s[4 * m], q[m].x, o0);
-            o1 = fmaf(s[4 * m + 1], q[m].y, o1);
-            o2 = fmaf(s[4 * m + 2], q[m].z, o2);
-            o3 = fmaf(s[4 * m + 3], q[m].w, o3);
-          }
-          o_pend = (o0 + o1) + (o2 + o3);
-        }
-      } else {
-        float4 k[M], q[M];
-        float vj = vb[jl];
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          k[m] = reinterpret_cast<const float4*>(base + Dp)[part + P * m];
-          q[m] = reinterpret_cast<const float4*>(base)[part + P * m];
-        }
-#pragma unroll 2
-        for (int t = 0; t < nt; ++t) {
-          float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll
-          for (int m = 0; m < M; ++m) {
-            s[4 * m] = fmaf(c_h, s[4 * m], k[m].x * vj);
-            s[4 * m + 1] = fmaf(c_h, s[4 * m + 1], k[m].y * vj);
-            s[4 * m + 2] = fmaf(c_h, s[4 * m + 2], k[m].z * vj);
-            s[4 * m + 3] = fmaf(c_h, s[4 * m + 3], k[m].w * vj);
-            o0 = fmaf(s[4 * m], q[m].x, o0);
-            o1 = fmaf(s[4 * m + 1], q[m].y, o1);
-            o2 = fmaf(s[4 * m + 2], q[m].z, o2);
-            o3 = fmaf(s[4 * m + 3], q[m].w, o3);
-          }
-          if (t + 1 < nt) {
-            const float4* qn = reinterpret_cast<const float4*>(base + (t + 1) * tok_floats);
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-              q[m] = qn[part + P * m];
-              k[m] = qn[Dp / 4 + part + P * m];
-            }
-            vj = vb[(t + 1) * cols_per_block + jl];
-          }
-          #pragma unroll
-          for (int off = P >> 1; off > 0; off >>= 1) o_pend += __shfl_xor_sync(0xffffffffu, o_pend, off);
-          if (t > 0 && part == 0 && owns) yo[(t - 1) * ldy] = o_pend;
-          o_pend = (o0 + o1) + (o2 + o3);
-        }
-      }
-      #pragma unroll
-          for (int off = P >> 1; off > 0; off >>= 1) o_pend += __shfl_xor_sync(0xffffffffu, o_pend, off);
-      if (part == 0 && owns) yo[(nt - 1) * ldy] = o_pend;
+      float* yg = y + (long long)t0 * ldy + (long long)h * VD + j;
+      int g = 0;
+      for (; g + REC_GROUP <= nt; g += REC_GROUP)
+        rec_group<DELTA, KPL, DP, true>(s, tok + g * tok_floats, vcol + g, yg + g * ldy, ldy, REC_GROUP, part, owns, c_h);
+      if (g < nt) rec_group<DELTA, KPL, DP, false>(s, tok + g * tok_floats, vcol + g, yg + g * ldy, ldy, nt - g, part, owns, c_h);
     }
     __syncthreads();
   }
@@ -512,8 +521,8 @@ extern "C" int tl_recurrence_scan(const float* proj, long long ld, int q_col, in
                                                                     key_eps, silu_inputs, prep, vact, H, D, VD, Dp, pairs);
     TL_LAUNCH_CHECK();
     // tokens a stage: as many (16 at most) as 96 KB hold in three stages
-    int TC = 16;
-    auto bytes = [&](int tc) { return (size_t)REC_STAGES * tc * (narr * Dp + cols_per_block) * sizeof(float); };
+    int TC = REC_CHUNK;
+    auto bytes = [&](int tc) { return (size_t)REC_STAGES * (tc * narr * Dp + REC_CHUNK * cols_per_block) * sizeof(float); };
     while (TC > 1 && bytes(TC) > 96 * 1024) TC >>= 1;
     const size_t smem = bytes(TC);
     const float* vsrc = delta ? proj : vact;
@@ -525,7 +534,7 @@ extern "C" int tl_recurrence_scan(const float* proj, long long ld, int q_col, in
       cudaFuncSetAttribute(recurrence_scan_staged_kernel<DELTA_, KPL_, DP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
                            96 * 1024);                                                                                          \
     recurrence_scan_staged_kernel<DELTA_, KPL_, DP_><<<grid, threads + 32, smem, stream>>>(                                     \
-        prep, vsrc, ld_v, vc, head_decay, state, slot_floats, state_slot, row_start, y, H, D, VD, cols_per_block, TC,           \
+        prep, vsrc, ld_v, vc, head_decay, state, slot_floats, state_slot, row_start, y, rows, H, D, VD, cols_per_block, TC,           \
         write_state);                                                                                                           \
   } while (0)
 #define TL_RSS_D(DELTA_, DP_)                   \
