@@ -47,6 +47,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // the row so that the eight rows an ldmatrix reads fall into different banks.
 template <int N> __device__ __forceinline__ int swz(int row, int chunk) { return row * (N * 2) + ((chunk ^ (row & 7)) << 4); }
 
+// The CTAs of a thread-block cluster (a launch without one is a cluster of one CTA): how many, which one this is, the
+// barrier of all their threads, and a 32-bit float read from the same shared-memory place of another CTA.
+__device__ __forceinline__ uint32_t cluster_ctas() { uint32_t n; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n)); return n; }
+__device__ __forceinline__ uint32_t cluster_cta() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster(const float* mine, uint32_t cta) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(mine)), "r"(cta));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // c tanh(x / c) from one exponential: tanh(y) = 1 - 2 / (e^(2y) + 1), right at both ends (e^(2y) = inf gives 1, 0 gives -1)
 __device__ __forceinline__ float capped(float x, float cap, float inv_cap) {
   const float t = __expf(2.f * x * inv_cap);
@@ -95,6 +110,18 @@ __global__ void __launch_bounds__(128) attention_flex_mma_kernel(
   const int n_a = min(kt_first, (first_end + KT - 1) / KT);        // tiles of kept first tokens before the window's tiles
   const int n_tiles = n_a + kt_last - kt_first + 1;
   auto tile_of = [&](int it) { return it < n_a ? it : kt_first + (it - n_a); };
+  // a cluster shares the key tiles of its (request, KV head): CTA c takes the c-th stretch of them (decoding form only)
+  int it0 = 0, n_mine = n_tiles;
+  uint32_t n_cta = 1, cta = 0;
+  if constexpr (KEYSPLIT) {
+    n_cta = cluster_ctas();
+    cta = cluster_cta();
+    if (n_cta > 1) {
+      const int per = (n_tiles + (int)n_cta - 1) / (int)n_cta;
+      it0 = min(n_tiles, (int)cta * per);
+      n_mine = min(n_tiles, it0 + per) - it0;
+    }
+  }
 
   // ---- Q tile: M row m = (query row m / G, head m % G); rows past the tile's queries are zero ----
   for (int i = tid; i < QROWS * CHK; i += 128) {
@@ -135,7 +162,7 @@ __global__ void __launch_bounds__(128) attention_flex_mma_kernel(
   };
 #pragma unroll
   for (int s0 = 0; s0 < STAGES - 1; ++s0) {
-    if (s0 < n_tiles) load_kv(tile_of(s0), s0);
+    if (s0 < n_mine) load_kv(tile_of(it0 + s0), s0);
     cp_async_commit();
   }
 
@@ -156,11 +183,11 @@ __global__ void __launch_bounds__(128) attention_flex_mma_kernel(
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   uint32_t qf[D / 16][4];
 
-  for (int it = 0; it < n_tiles; ++it) {
-    const int kt = tile_of(it), stage = it % STAGES;
+  for (int it = 0; it < n_mine; ++it) {
+    const int kt = tile_of(it0 + it), stage = it % STAGES;
     cp_async_wait<STAGES - 2>();      // this thread's copies of tile `it` have landed
     __syncthreads();                  // everybody's have, and everybody is done with the tile before
-    if (it + STAGES - 1 < n_tiles) load_kv(tile_of(it + STAGES - 1), (it + STAGES - 1) % STAGES);
+    if (it + STAGES - 1 < n_mine) load_kv(tile_of(it0 + it + STAGES - 1), (it + STAGES - 1) % STAGES);
     cp_async_commit();
     if (!active) continue;            // a warp whose 16 M rows lie past the tile's queries only helps with the loads
     if (it == 0) {
@@ -308,6 +335,8 @@ __global__ void __launch_bounds__(128) attention_flex_mma_kernel(
     // ---- merge the four warps' shares of the keys, in warp order ----
     float* mo = reinterpret_cast<float*>(sk);              // [4][16][VD]
     float* mml = mo + 4 * 16 * VD;                         // [4][16][2]
+    float* co = mml + 4 * 16 * 2;                          // [16][VD]: this CTA's share, for the cluster's first CTA
+    float* cml = co + 16 * VD;                             // [16][2]
     __syncthreads();                                       // every warp is done with the key/value stages
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -342,7 +371,43 @@ __global__ void __launch_bounds__(128) attention_flex_mma_kernel(
         b0 += f * src[c + VD / 2];
         b1 += f * src[c + VD / 2 + 1];
       }
-      emit(r, c, a0, a1, b0, b1, l);
+      if (n_cta == 1) {
+        emit(r, c, a0, a1, b0, b1, l);
+      } else {
+        co[r * VD + c] = a0;
+        co[r * VD + c + 1] = a1;
+        co[r * VD + c + VD / 2] = b0;
+        co[r * VD + c + VD / 2 + 1] = b1;
+        if (c == 0) {
+          cml[r * 2] = mrow;
+          cml[r * 2 + 1] = l;
+        }
+      }
+    }
+    if (n_cta > 1) {
+      // ---- the cluster's CTAs' shares, in their order, by its first CTA out of the others' shared memory ----
+      cluster_sync();
+      if (cta == 0) {
+        for (int i = tid; i < 16 * (VD / 4); i += 128) {
+          const int r = i / (VD / 4), c = (i % (VD / 4)) * 2;
+          if (r >= nq * G) continue;
+          float mrow = -INFINITY;
+          for (uint32_t w = 0; w < n_cta; ++w) mrow = fmaxf(mrow, ld_cluster(cml + r * 2, w));
+          float l = 0.f, a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+          for (uint32_t w = 0; w < n_cta; ++w) {
+            const float mw = ld_cluster(cml + r * 2, w);
+            if (mw == -INFINITY) continue;
+            const float f = exp2f(mw - mrow);
+            l += f * ld_cluster(cml + r * 2 + 1, w);
+            a0 += f * ld_cluster(co + r * VD + c, w);
+            a1 += f * ld_cluster(co + r * VD + c + 1, w);
+            b0 += f * ld_cluster(co + r * VD + c + VD / 2, w);
+            b1 += f * ld_cluster(co + r * VD + c + VD / 2 + 1, w);
+          }
+          emit(r, c, a0, a1, b0, b1, l);
+        }
+      }
+      cluster_sync();        // nobody leaves while its shared memory may still be read
     }
   }
 }
@@ -350,9 +415,9 @@ __global__ void __launch_bounds__(128) attention_flex_mma_kernel(
 template <int D, int VD, bool KEYSPLIT, int STAGES>
 static int launch(const void* q, const void* k_cache, const void* v_cache, const int* block_table, int max_pages, int page_size,
                   int num_pages, const int* tiles, int n_tiles, const int* positions, const Options& opt, void* out, int Hq,
-                  int Hk, int* status, cudaStream_t stream) {
+                  int Hk, int cluster, int* status, cudaStream_t stream) {
   constexpr int SMEM = (KEYSPLIT ? 16 : 64) * D * 2 + STAGES * KT * (D + VD) * 2;
-  static_assert(!KEYSPLIT || 4 * 16 * (VD + 2) * 4 <= STAGES * KT * (D + VD) * 2, "the merge buffer reuses the stages");
+  static_assert(!KEYSPLIT || 5 * 16 * (VD + 2) * 4 <= STAGES * KT * (D + VD) * 2, "the merge buffer reuses the stages");
   static bool set = false;
   if (!set) {
     cudaError_t e = cudaFuncSetAttribute(attention_flex_mma_kernel<D, VD, KEYSPLIT, STAGES>,
@@ -364,6 +429,25 @@ static int launch(const void* q, const void* k_cache, const void* v_cache, const
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size;) ++page_shift;
   dim3 grid(n_tiles, Hk);
+  if (KEYSPLIT && cluster > 1) {
+    // a cluster of `cluster` CTAs along z shares a (request, KV head)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles, Hk, cluster);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = cluster;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_flex_mma_kernel<D, VD, KEYSPLIT, STAGES>, (const bf16*)q,
+                                       (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, page_size, page_shift,
+                                       num_pages, tiles, positions, opt, (bf16*)out, Hq, Hk, status);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+  }
   attention_flex_mma_kernel<D, VD, KEYSPLIT, STAGES><<<grid, 128, SMEM, stream>>>(
       (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, page_size, page_shift, num_pages, tiles,
       positions, opt, (bf16*)out, Hq, Hk, status);
@@ -387,13 +471,15 @@ extern "C" int tl_attention_flex_mma_tile_rows(int Hq, int Hk) {
 
 // tiles: int32 [n_tiles, 3] = (request index, first row, query rows <= tile rows), rows of a tile consecutive in position.
 // max_tile_rows: the most query rows any tile holds; when they and their heads fit 16 M rows, the form that splits the
-// keys among the warps runs. out: rows of ld_out bf16, 4-byte aligned; gate: rows of ld_gate bf16 or null.
+// keys among the warps runs; there, with few tiles and `max_context` keys to go through, clusters of up to 8 CTAs share a
+// (request, KV head)'s key tiles until the grid has a CTA an SM (`sm_count`), and the cluster's first CTA merges their shares
+// out of their shared memory. out: rows of ld_out bf16, 4-byte aligned; gate: rows of ld_gate bf16 or null.
 extern "C" int tl_attention_flex_mma(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                      int max_pages, int page_size, int num_pages, const int* tiles, int n_tiles,
                                      int max_tile_rows, const int* positions, float scale, float softcap, int window,
                                      int keep_first, const float* inv_freq_out, const void* gate, long long ld_gate,
                                      float out_scale, void* out, long long ld_out, int rows, int Hq, int Hk, int D, int VD,
-                                     int* status, cudaStream_t stream) {
+                                     int max_context, int sm_count, int* status, cudaStream_t stream) {
   if (rows == 0 || n_tiles == 0) return 0;
   TL_REQUIRE(tl_attention_flex_mma_supported(Hq, Hk, D, VD), "attention (tensor cores): %d heads over %d KV heads, keys of %d, values of %d",
              Hq, Hk, D, VD);
@@ -405,9 +491,16 @@ extern "C" int tl_attention_flex_mma(const void* q, const void* k_cache, const v
   TL_REQUIRE(((uintptr_t)out % 4) == 0 && ld_out % 2 == 0, "attention: output rows of %lld entries must start on 4 bytes", ld_out);
   fx::Options opt{scale, softcap, out_scale, window, keep_first, inv_freq_out, (const bf16*)gate, ld_gate, ld_out};
   const bool keysplit = max_tile_rows * (Hq / Hk) <= 16;
+  int cluster = 1;
+  if (keysplit) {
+    const int reach = window > 0 ? (max_context < window + keep_first + fx::KT ? max_context : window + keep_first + fx::KT) : max_context;
+    const int key_tiles = (reach + fx::KT - 1) / fx::KT;
+    const long long ctas = (long long)n_tiles * Hk;
+    while (cluster < 8 && 2 * cluster <= key_tiles && ctas * cluster < (sm_count > 0 ? sm_count : 148)) cluster *= 2;
+  }
 #define TL_FX(D_, VD_, KS_, ST_)                                                                                              \
   fx::launch<D_, VD_, KS_, ST_>(q, k_cache, v_cache, block_table, max_pages, page_size, num_pages, tiles, n_tiles, positions, \
-                                opt, out, Hq, Hk, status, stream)
+                                opt, out, Hq, Hk, cluster, status, stream)
   if (D == 64 && VD == 64) return keysplit ? TL_FX(64, 64, true, 4) : TL_FX(64, 64, false, 3);
   if (D == 64) return keysplit ? TL_FX(64, 128, true, 3) : TL_FX(64, 128, false, 2);
   if (VD == 64) return keysplit ? TL_FX(128, 64, true, 3) : TL_FX(128, 64, false, 2);

@@ -126,8 +126,8 @@ def lib():
         l.tl_attention_flex_mma_tile_rows.restype = c_int
         l.tl_attention_flex_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
                                             c_void_p, ctypes.c_float, ctypes.c_float, c_int, c_int, c_void_p, c_void_p, c_longlong,
-                                            ctypes.c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                            c_void_p]
+                                            ctypes.c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                            c_void_p, c_void_p]
         l.tl_attention_flex_mma.restype = c_int
         l.tl_gemm_skinny_supported.argtypes = [c_int, c_int, c_int, c_longlong, c_longlong]
         l.tl_gemm_skinny_supported.restype = c_int
@@ -568,7 +568,8 @@ def _attention_flex(self, part, q, cache, table, step, gate, ld_gate: int, out_s
             q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
             cache.k.shape[0], tiles.data_ptr(), tiles.shape[0], int(most), step.positions.data_ptr(), float(part.scale),
             float(part.softcap or 0.0), int(part.window or 0), int(part.keep_first or 0), ops.ptr(part.inv_freq_v), ops.ptr(gate),
-            int(ld_gate), float(out_scale), out.data_ptr(), out.stride(0), R, Hq, Hk, D, VD, self.status.data_ptr(), ops.stream())
+            int(ld_gate), float(out_scale), out.data_ptr(), out.stride(0), R, Hq, Hk, D, VD, int(step.max_context), ops.sm_count(),
+            self.status.data_ptr(), ops.stream())
         _check(code, "attention_flex_mma")
     return True
 

@@ -202,6 +202,30 @@ def test_gated_attention_reaches_a_far_key_among_hundreds(dtype, H, G, D, VD, di
         assert rel(got, want) < TOL[dtype], (row, key)
 
 
+@pytest.mark.parametrize("mask,cap", [(None, None), ((600, 3), 30.0), ((130, 70), None)])
+@pytest.mark.parametrize("H,G,D,VD", [(4, 2, 64, 64), (8, 1, 128, 64), (2, 2, 64, 128)])
+def test_decoding_behind_many_key_tiles(H, G, D, VD, mask, cap):
+    """Rows decoded alone behind 800 keys (bfloat16): few requests and many key tiles, so several CTAs share a request's
+    keys and their shares are merged. A key far back stands out, then the key at the window's edge."""
+    width, T = 40, 800
+    layer = C._attn(H, G, D, VD, 0.15, C._rot(3000.0, D // 2), mask, cap)
+    spec, W, pre = one_layer(layer, width, seed=H + D)
+    m = layer["mixer"]
+    g = torch.Generator().manual_seed(3)
+    x0 = (torch.randn(T, width, generator=g) * 0.5).to(torch.bfloat16).float()
+    rt = rt_of("bfloat16")
+    row = T - 1
+    for key in (1, row - mask[0] + 1 if mask else 400):
+        x, Wk = spiked(x0, W, pre + "mix.", m, row, key, ((0.8 * cap if cap else 10.0) / 0.15) ** 0.5)
+        w64 = {k: v.double().numpy() for k, v in Wk.items()}
+        want = P.mixer_attention(x.double().numpy(), m, w64, pre + "mix.", None)
+        part = bound(spec, 0, Wk, rt, width)
+        cache, step = stepper([part.cache_need()], rt, pages=64)
+        got = in_portions(part, x.to(torch.bfloat16), cache, step, [T - 12] + [1] * 12)
+        assert rel(got[T - 12:], want[T - 12:]) < TOL["bfloat16"], (key,)
+        assert int(rt.status.item()) == 0
+
+
 def _half(spec, which, pre, width, W, rt):
     from tandemllm_b200.parts import make_part
     part = make_part("mixer", spec.layers[0].mixer["mixers"][which], prefix=pre, hidden_size=width)
