@@ -5,6 +5,9 @@ from .lfm2_moe import MODEL_TYPES as _LFM2_TYPES
 from .lfm2_moe import Lfm2MoeConfig
 from .registry import (REGISTRY, Architecture, architecture_of, read_model_config, register, resolve_model_folder,
                        spec_of, unregister)
+from .niralix import ARCHITECTURES as _NIRALIX_ARCHS
+from .niralix import MODEL_TYPES as _NIRALIX_TYPES
+from .niralix import NiralixConfig
 from .puripel import ARCHITECTURES as _PURIPEL_ARCHS
 from .puripel import MODEL_TYPES as _PURIPEL_TYPES
 from .puripel import PuripelConfig
@@ -28,6 +31,9 @@ register(Architecture(name="puripel", architectures=_PURIPEL_ARCHS, model_types=
 register(Architecture(name="sebilorn", architectures=_SEBILORN_ARCHS, model_types=_SEBILORN_TYPES,
                       read_config=SebilornConfig.from_dict))
 
-__all__ = ["PuripelConfig", "SebilornConfig", "REGISTRY", "Architecture", "architecture_of", "read_model_config", "register", "unregister",
+register(Architecture(name="niralix", architectures=_NIRALIX_ARCHS, model_types=_NIRALIX_TYPES,
+                      read_config=NiralixConfig.from_dict))
+
+__all__ = ["NiralixConfig", "PuripelConfig", "SebilornConfig", "REGISTRY", "Architecture", "architecture_of", "read_model_config", "register", "unregister",
            "resolve_model_folder", "spec_of", "LayerSpec", "ModelSpec", "PartSpec", "Site", "StreamAdd", "plain_schedule",
            "Lfm2MoeConfig", "SifupelConfig"]

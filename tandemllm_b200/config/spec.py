@@ -47,6 +47,7 @@ class LayerSpec:
     arrangement: str = "prenorm_residual"
     mixer_post_norm: PartSpec | None = None            # arrangements that norm a branch's output as well
     feed_forward_post_norm: PartSpec | None = None
+    arrangement_params: Mapping[str, Any] | None = None    # an arrangement with sizes and tensors of its own reads them here
 
 
 @dataclass(frozen=True)
@@ -79,6 +80,10 @@ class ModelSpec:
     final_norm_prefix: str = field(kw_only=True)    # the last norm's part of its tensors' names
     head_name: str | None = None           # None: the head is the embedding (tied)
     embedding_scale: float = 1.0           # every embedded row is multiplied by this (32-bit)
+    logit_scale: float = 1.0               # the head's logits are multiplied by this (32-bit)
+    streams: int = 0                       # > 0: the residual is this many streams [streams, rows, hidden] that start as the
+                                           # embedded row and are summed in front of the last norm; the layers' arrangement
+                                           # says how sublayers read and rewrite them. 0: one plain residual
     logit_softcap: float | None = None     # c: logits <- c tanh(logits / c); None: the logits stay as the head made them
     ignored_names: tuple[str, ...] = ()    # stored tensors that are neither read nor an error (a tied model's copy
                                            # of its head, for one)

@@ -3,7 +3,10 @@
 //
 //   tl_qkv_rotate_store   one row a block: q, k (first `rot` entries of a head turned by the row's position, halves
 //                         layout: entry i with entry i + rot / 2) and v (optionally turned over all its entries with
-//                         frequencies of its own) from one fused product; q to a plain tensor, k and v into their pages
+//                         frequencies of its own) from one fused product; q to a plain tensor, k and v into their pages.
+//                         The sines and cosines of q and k may carry a common factor (a stretched rotation's magnitude);
+//                         v may first be blended with another tensor's values of the same row, (1 - l) v + l v_other, l a
+//                         number on the device (values carried over from an earlier layer)
 //   tl_attention_flex     one warp a (row, query head): score = scale q.k, optionally capped (c tanh(score / c)); row at
 //                         position i sees key j <= i when there is no window, or i - j < window, or j < keep_first;
 //                         softmax in 32-bit; the output optionally turned back by the row's own position (the inverse of
@@ -32,12 +35,17 @@ __global__ void __launch_bounds__(128) qkv_rotate_store_kernel(
     const T* __restrict__ qkv, long long ld, int q_col, int k_col, int v_col, const float* __restrict__ inv_freq, int rot,
     const float* __restrict__ inv_freq_v, const int* __restrict__ positions, const int* __restrict__ req_of_row,
     const int* __restrict__ block_table, int max_pages, int page_size, int num_pages, T* __restrict__ q_out,
-    T* __restrict__ k_cache, T* __restrict__ v_cache, int Hq, int Hk, int D, int VD, int* __restrict__ status) {
+    T* __restrict__ k_cache, T* __restrict__ v_cache, int Hq, int Hk, int D, int VD, int* __restrict__ status,
+    float rot_magnitude, const T* __restrict__ v_other, long long ld_other, const float* __restrict__ v_blend) {
   __shared__ float sn[FLEX_MAX_DIM / 2], cs[FLEX_MAX_DIM / 2], snv[FLEX_MAX_DIM / 2], csv[FLEX_MAX_DIM / 2];
   const int r = blockIdx.x;
   const int pos = positions[r];
   const int half = inv_freq ? rot / 2 : 0, vhalf = inv_freq_v ? VD / 2 : 0;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+    sn[i] *= rot_magnitude;
+    cs[i] *= rot_magnitude;
+  }
   for (int i = threadIdx.x; i < vhalf; i += blockDim.x) sincosf((float)pos * inv_freq_v[i], &snv[i], &csv[i]);
   __syncthreads();
   const T* row = qkv + (long long)r * ld;
@@ -56,6 +64,16 @@ __global__ void __launch_bounds__(128) qkv_rotate_store_kernel(
   for (int e = threadIdx.x; e < Hk * D; e += blockDim.x) {
     const int h = e / D, i = e - h * D;
     k_cache[(at + (long long)h * page_size) * D + i] = from_f32<T>(rotated_entry(row + k_col + h * D, i, half, sn, cs));
+  }
+  if (v_other) {
+    // blended in 32-bit from the two stored values, rounded once; a blended value is not turned as well
+    const float l = *v_blend;
+    const T* other = v_other + (long long)r * ld_other;
+    for (int e = threadIdx.x; e < Hk * VD; e += blockDim.x) {
+      const int h = e / VD, i = e - h * VD;
+      v_cache[(at + (long long)h * page_size) * VD + i] = from_f32<T>((1.f - l) * to_f32(row[v_col + e]) + l * to_f32(other[e]));
+    }
+    return;
   }
   for (int e = threadIdx.x; e < Hk * VD; e += blockDim.x) {
     const int h = e / VD, i = e - h * VD;
@@ -165,8 +183,10 @@ extern "C" int tl_qkv_rotate_store(const void* qkv, long long ld, int q_col, int
                                    int rot, const float* inv_freq_v, const int* positions, const int* req_of_row,
                                    const int* block_table, int max_pages, int page_size, int num_pages, void* q_out,
                                    void* k_cache, void* v_cache, int rows, int Hq, int Hk, int D, int VD, int dtype,
-                                   int* status, cudaStream_t stream) {
+                                   int* status, float rot_magnitude, const void* v_other, long long ld_other,
+                                   const float* v_blend, cudaStream_t stream) {
   if (rows == 0) return 0;
+  TL_REQUIRE(!v_other || (v_blend && !inv_freq_v), "qkv_rotate_store: blended values want their weight and are not turned");
   TL_REQUIRE(Hq > 0 && Hk > 0 && D >= 1 && D <= FLEX_MAX_DIM && VD >= 1 && VD <= FLEX_MAX_DIM,
              "qkv_rotate_store: %d query heads, %d KV heads, key size %d, value size %d (sizes up to %d)", Hq, Hk, D, VD,
              FLEX_MAX_DIM);
@@ -177,7 +197,8 @@ extern "C" int tl_qkv_rotate_store(const void* qkv, long long ld, int q_col, int
 #define TL_QRS(T_)                                                                                                         \
   qkv_rotate_store_kernel<T_><<<rows, 128, 0, stream>>>((const T_*)qkv, ld, q_col, k_col, v_col, inv_freq, rot, inv_freq_v,  \
                                                         positions, req_of_row, block_table, max_pages, page_size, num_pages, \
-                                                        (T_*)q_out, (T_*)k_cache, (T_*)v_cache, Hq, Hk, D, VD, status)
+                                                        (T_*)q_out, (T_*)k_cache, (T_*)v_cache, Hq, Hk, D, VD, status,    \
+                                                        rot_magnitude, (const T_*)v_other, ld_other, v_blend)
   if (dtype == TL_FP32) TL_QRS(float);
   else TL_QRS(bf16);
 #undef TL_QRS

@@ -13,7 +13,9 @@
 //   attention_latent  per (row, head): softmax over the visible keys j (0 <= pos - j < window, or all) of scale * q' . key_j,
 //                     in 32-bit with a running maximum; out[r, h, :L] = sum_j p_j c_j. Keys are taken in tiles of 32 aligned
 //                     to absolute positions, so the order of additions does not depend on how the sequence was cut into
-//                     steps, what else is in the batch or which pages hold the keys.
+//                     steps, what else is in the batch or which pages hold the keys. With `sinks` (a number a head) the
+//                     softmax denominator also holds exp(sink): a share of the weight that has no key and no value.
+//                     head_linear may multiply its result entry by entry by sigmoid(gate) (an output gate).
 #include "common.cuh"
 
 namespace tl {
@@ -104,7 +106,8 @@ constexpr int HL_ROWS = 16, HL_COLS = 64, HL_K = 32;
 template <typename T, typename TO>
 __global__ void __launch_bounds__(256) head_linear_kernel(const T* __restrict__ a, long long ld_a, long long a_head,
                                                           const T* __restrict__ w, TO* __restrict__ out, long long ld_out,
-                                                          long long out_head, int rows, int N, int K) {
+                                                          long long out_head, int rows, int N, int K,
+                                                          const T* __restrict__ gate, long long ld_gate) {
   __shared__ float sA[HL_ROWS][HL_K];
   __shared__ float sW[HL_COLS][HL_K + 1];
   const int h = blockIdx.z, r0 = blockIdx.y * HL_ROWS, n0 = blockIdx.x * HL_COLS;
@@ -131,7 +134,12 @@ __global__ void __launch_bounds__(256) head_linear_kernel(const T* __restrict__ 
   if (n0 + tn < N)
 #pragma unroll
     for (int i = 0; i < 4; ++i)
-      if (r0 + tr + i < rows) out[(long long)(r0 + tr + i) * ld_out + (long long)h * out_head + n0 + tn] = from_f32<TO>(acc[i]);
+      if (r0 + tr + i < rows) {
+        float v = acc[i];
+        // (gate [rows, H * N] logits, rows ld_gate apart: the result times their sigmoid)
+        if (gate) v *= 1.f / (1.f + expf(-to_f32(gate[(long long)(r0 + tr + i) * ld_gate + (long long)h * N + n0 + tn])));
+        out[(long long)(r0 + tr + i) * ld_out + (long long)h * out_head + n0 + tn] = from_f32<TO>(v);
+      }
 }
 
 constexpr int LA_WARPS = 8;     // heads a block: a warp a head
@@ -142,7 +150,7 @@ template <typename T, int LPER>
 __global__ void __launch_bounds__(LA_WARPS * 32) attention_latent_kernel(
     const float* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ table, int max_pages, int page_size,
     int num_pages, const int* __restrict__ req_of_row, const int* __restrict__ positions, float scale, int window,
-    T* __restrict__ out, int H, int L, int Dk, int* __restrict__ status) {
+    T* __restrict__ out, int H, int L, int Dk, int* __restrict__ status, const float* __restrict__ sinks) {
   extern __shared__ __align__(16) float sm[];
   const int ldk = Dk + 1;                             // a key's row in shared memory, padded against bank conflicts
   float* sK = sm;                                     // [TILE][ldk]
@@ -209,7 +217,13 @@ __global__ void __launch_bounds__(LA_WARPS * 32) attention_latent_kernel(
     }
   }
   if (head) {
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float keep = 1.f;
+    if (sinks) {
+      const float sk = sinks[h], top = fmaxf(m, sk);
+      keep = m == -INFINITY ? 0.f : expf(m - top);
+      l = l * keep + expf(sk - top);
+    }
+    const float inv = (l > 0.f ? 1.f / l : 0.f) * keep;
     T* o = out + ((long long)r * H + h) * L;
 #pragma unroll
     for (int i = 0; i < LPER; ++i) {
@@ -222,7 +236,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) attention_latent_kernel(
 template <typename T>
 static int launch_latent(const float* q, const void* cache, const int* table, int max_pages, int page_size, int num_pages,
                          const int* req_of_row, const int* positions, float scale, int window, void* out, int rows, int H, int L,
-                         int Dk, int* status, cudaStream_t stream) {
+                         int Dk, int* status, const float* sinks, cudaStream_t stream) {
   const dim3 grid(rows, ceil_div(H, LA_WARPS)), block(LA_WARPS * 32);
   const size_t smem = (size_t)(LA_TILE * (Dk + 1) + LA_WARPS * Dk) * sizeof(float);
   const int per = ceil_div(L, 32);
@@ -232,7 +246,7 @@ static int launch_latent(const float* q, const void* cache, const int* table, in
       cudaFuncSetAttribute(attention_latent_kernel<T, LPER_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
     attention_latent_kernel<T, LPER_><<<grid, block, smem, stream>>>(q, (const T*)cache, table, max_pages, page_size, num_pages, \
                                                                      req_of_row, positions, scale, window, (T*)out, H, L, Dk,    \
-                                                                     status);                                                    \
+                                                                     status, sinks);                                             \
   } while (0)
   if (per <= 1) TL_LATENT(1);
   else if (per <= 2) TL_LATENT(2);
@@ -288,14 +302,15 @@ extern "C" int tl_rmsnorm_rows(const void* in, long long ld_in, const float* w, 
 // out[r * ld_out + h * out_head + n] = sum_k a[r * ld_a + h * a_head + k] * w[(h * N + n) * K + k]; a and w of `dtype`, out of
 // `out_dtype`.
 extern "C" int tl_head_linear(const void* a, long long ld_a, long long a_head, const void* w, void* out, long long ld_out,
-                              long long out_head, int rows, int H, int N, int K, int dtype, int out_dtype, cudaStream_t stream) {
+                              long long out_head, int rows, int H, int N, int K, int dtype, int out_dtype, const void* gate,
+                              long long ld_gate, cudaStream_t stream) {
   if (rows == 0) return 0;
   TL_REQUIRE(rows > 0 && H > 0 && H <= 65535 && N > 0 && K > 0, "head product: %d rows, %d heads, %d x %d", rows, H, N, K);
   TL_REQUIRE(ceil_div(rows, HL_ROWS) <= 65535, "head product: %d rows in one launch", rows);
   const dim3 grid(ceil_div(N, HL_COLS), ceil_div(rows, HL_ROWS), H);
 #define TL_HL(T_, TO_)                                                                                                      \
   head_linear_kernel<T_, TO_><<<grid, 256, 0, stream>>>((const T_*)a, ld_a, a_head, (const T_*)w, (TO_*)out, ld_out, out_head, \
-                                                        rows, N, K)
+                                                        rows, N, K, (const T_*)gate, ld_gate)
   if (dtype == TL_FP32) {
     TL_REQUIRE(out_dtype == TL_FP32, "head product: 32-bit operands give a 32-bit result");
     TL_HL(float, float);
@@ -312,7 +327,7 @@ extern "C" int tl_head_linear(const void* a, long long ld_a, long long a_head, c
 // q float [rows, H, Dk] (Dk = L + the rotated part); cache [pages, 1, page_size, Dk]; out [rows, H, L] of the cache's type.
 extern "C" int tl_attention_latent(const float* q, const void* cache, const int* table, int max_pages, int page_size,
                                    int num_pages, const int* req_of_row, const int* positions, float scale, int window, void* out,
-                                   int rows, int H, int L, int Dk, int dtype, int* status, cudaStream_t stream) {
+                                   int rows, int H, int L, int Dk, int dtype, int* status, const float* sinks, cudaStream_t stream) {
   if (rows == 0) return 0;
   TL_REQUIRE(rows > 0 && H > 0 && H <= 65535 * LA_WARPS && L > 0 && Dk >= L, "latent attention: %d rows, %d heads, latent %d of %d",
              rows, H, L, Dk);
@@ -321,7 +336,7 @@ extern "C" int tl_attention_latent(const float* q, const void* cache, const int*
   TL_REQUIRE(window >= 0 && page_size > 0, "latent attention: window %d, pages of %d", window, page_size);
   if (dtype == TL_FP32)
     return launch_latent<float>(q, cache, table, max_pages, page_size, num_pages, req_of_row, positions, scale, window, out, rows,
-                                H, L, Dk, status, stream);
+                                H, L, Dk, status, sinks, stream);
   return launch_latent<bf16>(q, cache, table, max_pages, page_size, num_pages, req_of_row, positions, scale, window, out, rows, H,
-                             L, Dk, status, stream);
+                             L, Dk, status, sinks, stream);
 }

@@ -35,7 +35,19 @@ struct LatentMmaParams {
   int requests, H, L, Dk, Dkp, qs;      // Dkp: Dk rounded up to 16; qs: elements of a staged row (Dkp + 8)
   int n_spans, span_keys;
   int* status;
+  const float* sinks;        // [H] or null: a head's softmax denominator also holds exp(sink), which has no key and no value
 };
+
+// What a row's sums are multiplied by and the reciprocal of its denominator, from its maximum m and sum l and the head's sink.
+__device__ __forceinline__ void latent_finish(float m, float l, const float* sinks, int h, float* keep, float* inv) {
+  *keep = 1.f;
+  if (sinks) {
+    const float sk = sinks[h], top = fmaxf(m, sk);
+    *keep = m == -INFINITY ? 0.f : expf(m - top);
+    l = l * *keep + expf(sk - top);
+  }
+  *inv = l > 0.f ? 1.f / l : 0.f;
+}
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -272,7 +284,9 @@ __global__ void __launch_bounds__(128 * CPB) latent_mma_kernel(LatentMmaParams p
     if (f >= pairs) continue;
     const long long pair = (long long)row_base * H + f;
     if (p.n_spans == 1) {
-      const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+      float keep, inv;
+      latent_finish(m_run[r], l_run[r], p.sinks, (int)(pair % H), &keep, &inv);
+      inv *= keep;
 #pragma unroll
       for (int n = 0; n < NT; ++n)
 #pragma unroll
@@ -300,7 +314,8 @@ __global__ void __launch_bounds__(128 * CPB) latent_mma_kernel(LatentMmaParams p
 // grid (rows * H), 128 threads: the spans of a pair joined in ascending order
 __global__ void __launch_bounds__(128) latent_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                           const int* __restrict__ positions, int window, bf16* __restrict__ out,
-                                                          int H, int L, int n_spans, int span_keys) {
+                                                          int H, int L, int n_spans, int span_keys,
+                                                          const float* __restrict__ sinks) {
   const long long pair = blockIdx.x;
   const int pos = positions[pair / H];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -312,7 +327,9 @@ __global__ void __launch_bounds__(128) latent_join_kernel(const float* __restric
     const float ms = part_ml[(pair * n_spans + s) * 2];
     if (ms != -INFINITY) sum += expf(ms - m) * part_ml[(pair * n_spans + s) * 2 + 1];
   }
-  const float inv = sum > 0.f ? 1.f / sum : 0.f;
+  float keep, inv;
+  latent_finish(m, sum, sinks, (int)(pair % H), &keep, &inv);
+  inv *= keep;
   for (int c = threadIdx.x; c < L; c += blockDim.x) {
     float acc = 0.f;
     for (int s = s0; s <= s1; ++s) {
@@ -340,7 +357,7 @@ extern "C" int tl_attention_latent_mma(const float* q, const void* cache, const 
                                        int num_pages, const int* req_of_row, const int* row_start, const int* positions,
                                        float scale, int window,
                                        void* out, float* scratch, int rows, int requests, int tiles, int H, int L, int Dk,
-                                       int n_spans, int span_keys, int* status, cudaStream_t stream) {
+                                       int n_spans, int span_keys, int* status, const float* sinks, cudaStream_t stream) {
   if (rows == 0) return 0;
   TL_REQUIRE(rows > 0 && requests > 0 && tiles > 0 && H > 0 && L > 0 && Dk >= L, "latent attention: %d rows of %d requests, %d "
              "heads, latent %d of %d", rows, requests, H, L, Dk);
@@ -352,7 +369,7 @@ extern "C" int tl_attention_latent_mma(const float* q, const void* cache, const 
   p.req_of_row = req_of_row; p.row_start = row_start; p.positions = positions; p.scale = scale; p.window = window; p.out = (bf16*)out;
   p.part_o = scratch; p.part_ml = scratch ? scratch + (long long)rows * H * n_spans * L : nullptr;
   p.requests = requests; p.H = H; p.L = L; p.Dk = Dk; p.Dkp = ceil_div(Dk, 16) * 16; p.qs = p.Dkp + 8;
-  p.n_spans = n_spans; p.span_keys = span_keys; p.status = status;
+  p.n_spans = n_spans; p.span_keys = span_keys; p.status = status; p.sinks = sinks;
   const int nt_all = ceil_div(L, 8);
   const int nt = nt_all <= 4 ? 4 : nt_all <= 8 ? 8 : nt_all <= 16 ? 16 : 32;
   const int chunks = ceil_div(nt_all, nt);
@@ -374,7 +391,7 @@ extern "C" int tl_attention_latent_mma(const float* q, const void* cache, const 
 #undef TL_LM
   TL_LAUNCH_CHECK();
   if (n_spans > 1) {
-    latent_join_kernel<<<rows * H, 128, 0, stream>>>(p.part_o, p.part_ml, positions, window, (bf16*)out, H, L, n_spans, span_keys);
+    latent_join_kernel<<<rows * H, 128, 0, stream>>>(p.part_o, p.part_ml, positions, window, (bf16*)out, H, L, n_spans, span_keys, sinks);
     TL_LAUNCH_CHECK();
   }
   return 0;

@@ -157,7 +157,8 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 #define TL_ACT_CLAMPED_SWISH 6   // a gate form of its own: g' = min(g, a0), u' = clamp(u, -a0, a0); g' sigmoid(a1 g') (u' + 1)
 #define TL_ACT_SOFTCAP 7     // a0 tanh(z / a0): a soft cap on scores or logits (an activation only, never a gate)
 #define TL_ACT_TANH 8        // tanh(z) (an activation only, never a gate)
-#define TL_ACT_LAST 8
+#define TL_ACT_SCALE 9       // a0 z (an activation only, never a gate)
+#define TL_ACT_LAST 9
 
 __device__ __forceinline__ float gate_activation(float g, int act) {
   switch (act) {
@@ -172,6 +173,7 @@ __device__ __forceinline__ float activation(float z, int act, float a0, float a1
   if (act == TL_ACT_XIELU) return z > 0.f ? fmaf(a0 * z, z, 0.5f * z) : fmaf(a1, expm1f(z) - z, 0.5f * z);
   if (act == TL_ACT_SOFTCAP) return a0 * tanhf(z / a0);
   if (act == TL_ACT_TANH) return tanhf(z);
+  if (act == TL_ACT_SCALE) return a0 * z;
   return gate_activation(z, act);
 }
 __device__ __forceinline__ float gated(float g, float u, int act) { return gate_activation(g, act) * u; }

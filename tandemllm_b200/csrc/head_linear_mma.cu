@@ -21,7 +21,8 @@ __device__ __forceinline__ void hm_mma(float (&d)[4], const uint32_t (&a)[4], ui
 template <typename TO>
 __global__ void __launch_bounds__(128) head_linear_mma_kernel(const bf16* __restrict__ a, long long ld_a, long long a_head,
                                                               const bf16* __restrict__ w, TO* __restrict__ out, long long ld_out,
-                                                              long long out_head, int rows, int N, int K, int vec) {
+                                                              long long out_head, int rows, int N, int K, int vec,
+                                                              const bf16* __restrict__ gate, long long ld_gate) {
   __shared__ __align__(16) bf16 sA[HM_TILE][HM_LD];
   __shared__ __align__(16) bf16 sW[HM_TILE][HM_LD];
   const int h = blockIdx.z, r0 = blockIdx.y * HM_TILE, n0 = blockIdx.x * HM_TILE;
@@ -79,7 +80,12 @@ __global__ void __launch_bounds__(128) head_linear_mma_kernel(const bf16* __rest
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int col = n0 + n * 8 + 2 * t + e;
-        if (col < N) o[col] = from_f32<TO>(acc[n][2 * r + e]);
+        if (col < N) {
+          float v = acc[n][2 * r + e];
+          // (gate [rows, H * N] logits, rows ld_gate apart: the result times their sigmoid)
+          if (gate) v *= 1.f / (1.f + expf(-to_f32(gate[(long long)row * ld_gate + (long long)h * N + col])));
+          o[col] = from_f32<TO>(v);
+        }
       }
   }
 }
@@ -89,9 +95,10 @@ __global__ void __launch_bounds__(128) head_linear_mma_kernel(const bf16* __rest
 using namespace tl;
 
 // out[r * ld_out + h * out_head + n] = sum_k a[r * ld_a + h * a_head + k] * w[(h * N + n) * K + k]; a, w bfloat16; out bfloat16
-// or float32 (`out_dtype`).
+// or float32 (`out_dtype`). `gate` (bfloat16 logits [rows, H * N], rows ld_gate apart; may be null): out times sigmoid(gate).
 extern "C" int tl_head_linear_mma(const void* a, long long ld_a, long long a_head, const void* w, void* out, long long ld_out,
-                                  long long out_head, int rows, int H, int N, int K, int out_dtype, cudaStream_t stream) {
+                                  long long out_head, int rows, int H, int N, int K, int out_dtype, const void* gate,
+                                  long long ld_gate, cudaStream_t stream) {
   if (rows == 0) return 0;
   TL_REQUIRE(rows > 0 && H > 0 && H <= 65535 && N > 0 && K > 0, "head product: %d rows, %d heads, %d x %d", rows, H, N, K);
   TL_REQUIRE(ceil_div(rows, HM_TILE) <= 65535, "head product: %d rows in one launch", rows);
@@ -99,10 +106,10 @@ extern "C" int tl_head_linear_mma(const void* a, long long ld_a, long long a_hea
   const dim3 grid(ceil_div(N, HM_TILE), ceil_div(rows, HM_TILE), H);
   if (out_dtype == TL_FP32)
     head_linear_mma_kernel<float><<<grid, 128, 0, stream>>>((const bf16*)a, ld_a, a_head, (const bf16*)w, (float*)out, ld_out,
-                                                            out_head, rows, N, K, vec);
+                                                            out_head, rows, N, K, vec, (const bf16*)gate, ld_gate);
   else
     head_linear_mma_kernel<bf16><<<grid, 128, 0, stream>>>((const bf16*)a, ld_a, a_head, (const bf16*)w, (bf16*)out, ld_out,
-                                                           out_head, rows, N, K, vec);
+                                                           out_head, rows, N, K, vec, (const bf16*)gate, ld_gate);
   TL_LAUNCH_CHECK();
   return 0;
 }

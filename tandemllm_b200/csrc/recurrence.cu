@@ -3,6 +3,8 @@
 //   decayed outer products   S <- c_h S + k v^T                                   (a fixed decay a head)
 //   generalized delta rule   S <- diag(d) S - (a * u) (u^T S) + k v^T             (both terms read the old S)
 //                            d = exp(-rate * sigmoid(w + w0)), a = sigmoid(a' + a_b), u = k / sqrt(sum k^2 + key_eps)
+//   gated outer products     S <- diag(d) S + k v^T                               (a decay a key channel and token)
+//                            d = sigmoid(w + w0)^rate = exp(-rate * softplus(-(w + w0)))
 //   output                   o = S^T q   with the new S
 //
 // and the norm behind them: out = y / rms(y) over each of `groups` equal parts of a row, times a weight, times
@@ -31,24 +33,32 @@ constexpr int REC_THREADS = 256;
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float siluf_(float x) { return x / (1.f + expf(-x)); }
+// sigmoid(z)^rate without forming the sigmoid: exp(-rate * log(1 + e^-z)), the logarithm split so that neither e^-z nor e^z overflows
+__device__ __forceinline__ float sigmoid_powf_(float z, float rate) {
+  return expf(-rate * (fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)))));
+}
+
+constexpr int RULE_FIXED = 0, RULE_DELTA = 1, RULE_GATED = 2;
+__host__ __device__ constexpr int rec_arrays(int rule) { return rule == RULE_DELTA ? 5 : (rule == RULE_GATED ? 3 : 2); }
 
 // Dp = 16 P: D rounded up to what P lanes of 16 keys hold. Shared memory: REC_TOKENS x 5 (or 3) arrays of Dp floats, then
 // REC_TOKENS x VD_tile values.
-template <bool DELTA>
+template <int RULE>
 __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
     const float* __restrict__ proj, long long ld, int q_col, int k_col, int v_col, int a_col,
     const float* __restrict__ wl, long long ld_w, const float* __restrict__ w0, const float* __restrict__ a_bias,
-    const float* __restrict__ head_decay, float rate, float key_eps, int silu_inputs, float* __restrict__ state,
+    const float* __restrict__ head_decay, float rate, float key_eps, int silu_inputs, float q_scale, float* __restrict__ state,
     long long slot_floats, const int* __restrict__ state_slot, const int* __restrict__ row_start, float* __restrict__ y,
     int H, int D, int VD, int P, int cols_per_block, int write_state) {
   extern __shared__ __align__(16) float sm[];
   const int Dp = 16 * P;
-  constexpr int NARR = DELTA ? 5 : 2;
-  // arrays a token: q, k, and for the delta rule d, u, au
+  constexpr bool DELTA = RULE == RULE_DELTA, GATED = RULE == RULE_GATED;
+  constexpr int NARR = rec_arrays(RULE);
+  // arrays a token: q, k, a decay a channel d (delta rule, gated), and for the delta rule u, au
   float* s_q = sm;
   float* s_k = s_q + REC_TOKENS * Dp;
   float* s_d = s_k + REC_TOKENS * Dp;
-  float* s_u = s_d + (DELTA ? REC_TOKENS * Dp : 0);
+  float* s_u = s_d + (DELTA || GATED ? REC_TOKENS * Dp : 0);
   float* s_au = s_u + (DELTA ? REC_TOKENS * Dp : 0);
   float* s_v = sm + NARR * REC_TOKENS * Dp;          // [REC_TOKENS][cols_per_block]
 
@@ -59,7 +69,7 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
   const int r0 = row_start[b], r1 = row_start[b + 1];
   if (r1 <= r0) return;
   float* S = state + (long long)state_slot[b] * slot_floats + (long long)h * D * VD;
-  const float c_h = DELTA ? 0.f : head_decay[h];
+  const float c_h = RULE != RULE_FIXED ? 0.f : head_decay[h];
 
   float s[16];
 #pragma unroll
@@ -91,7 +101,7 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
             kv = siluf_(kv);
           }
         }
-        tq[i] = qv;
+        tq[i] = qv * q_scale;
         tk[i] = kv;
         ss = fmaf(kv, kv, ss);
       }
@@ -110,6 +120,10 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
           s_u[tw * Dp + i] = u;
           s_au[tw * Dp + i] = au;
         }
+      }
+      if (GATED) {
+        const float* wrow = wl + (long long)(t0 + tw) * ld_w + (long long)h * D;
+        for (int i = lane; i < Dp; i += 32) s_d[tw * Dp + i] = i < D ? sigmoid_powf_(wrow[i] + w0[h * D + i], rate) : 0.f;
       }
       for (int c = lane; c < cols_per_block; c += 32) {
         float vv = col0 + c < VD ? vrow[col0 + c] : 0.f;
@@ -150,6 +164,20 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
           o2 = fmaf(s[4 * m + 2], q.z, o2);
           o3 = fmaf(s[4 * m + 3], q.w, o3);
         }
+      } else if (GATED) {
+        const float4* d4 = reinterpret_cast<const float4*>(s_d + t * Dp);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const float4 d = d4[part + P * m], k = k4[part + P * m], q = q4[part + P * m];
+          s[4 * m] = fmaf(d.x, s[4 * m], k.x * vj);
+          s[4 * m + 1] = fmaf(d.y, s[4 * m + 1], k.y * vj);
+          s[4 * m + 2] = fmaf(d.z, s[4 * m + 2], k.z * vj);
+          s[4 * m + 3] = fmaf(d.w, s[4 * m + 3], k.w * vj);
+          o0 = fmaf(s[4 * m], q.x, o0);
+          o1 = fmaf(s[4 * m + 1], q.y, o1);
+          o2 = fmaf(s[4 * m + 2], q.z, o2);
+          o3 = fmaf(s[4 * m + 3], q.w, o3);
+        }
       } else {
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
@@ -180,14 +208,15 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(
   }
 }
 
-// One warp a (row, head): what the scan needs of a token, [H][rows][NARR][Dp] = q, k (activated), and for the delta rule
-// d, u, a * u; entries past D are zero (a head's tokens lie together, so a chunk of them is one stretch of memory). With `vact`, the activated values [rows][H * VD] as well.
-template <bool DELTA>
+// One warp a (row, head): what the scan needs of a token, [H][rows][NARR][Dp] = q, k (activated), a decay a channel d (delta rule,
+// gated), and for the delta rule u, a * u; entries past D are zero (a head's tokens lie together, so a chunk of them is one stretch of memory). With `vact`, the activated values [rows][H * VD] as well.
+template <int RULE>
 __global__ void __launch_bounds__(128) recurrence_prepare_kernel(
     const float* __restrict__ proj, long long ld, int q_col, int k_col, int v_col, int a_col, const float* __restrict__ wl,
     long long ld_w, const float* __restrict__ w0, const float* __restrict__ a_bias, float rate, float key_eps, int silu_inputs,
-    float* __restrict__ prep, float* __restrict__ vact, int H, int D, int VD, int Dp, long long pairs) {
-  constexpr int NARR = DELTA ? 5 : 2;
+    float q_scale, float* __restrict__ prep, float* __restrict__ vact, int H, int D, int VD, int Dp, long long pairs) {
+  constexpr bool DELTA = RULE == RULE_DELTA, GATED = RULE == RULE_GATED;
+  constexpr int NARR = rec_arrays(RULE);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long idx = (long long)blockIdx.x * 4 + warp;
   if (idx >= pairs) return;
@@ -207,9 +236,13 @@ __global__ void __launch_bounds__(128) recurrence_prepare_kernel(
         kv = siluf_(kv);
       }
     }
-    tq[i] = qv;
+    tq[i] = qv * q_scale;
     tk[i] = kv;
     ss = fmaf(kv, kv, ss);
+  }
+  if (GATED) {
+    const float* wrow = wl + r * ld_w + (long long)h * D;
+    for (int i = lane; i < Dp; i += 32) tq[2 * Dp + i] = i < D ? sigmoid_powf_(wrow[i] + w0[h * D + i], rate) : 0.f;
   }
   if (DELTA) {
     ss = warp_sum(ss);
@@ -270,10 +303,11 @@ __device__ __forceinline__ void rec_reduce_scatter(float (&v)[T], int part) {
 // outputs wait in registers and cross the lanes together. Everything a token needs lies at offsets the compiler knows
 // (`tok`: the lane's first four floats of the group's first prepared token; `vcol`: the column's values, a token a float),
 // so the group is straight-line code whose loads the compiler moves ahead of the chain.
-template <bool DELTA, int KPL, int DP, bool FULL>
+template <int RULE, int KPL, int DP, bool FULL>
 __device__ __forceinline__ void rec_group(float (&s)[KPL], const float* __restrict__ tok, const float* __restrict__ vcol,
                                           float* __restrict__ yg, long long ldy, int n, int part, bool owns, float c_h) {
-  constexpr int P = DP / KPL, M = KPL / 4, tok_floats = (DELTA ? 5 : 2) * DP, Q = DP / 4;
+  constexpr bool DELTA = RULE == RULE_DELTA, GATED = RULE == RULE_GATED;
+  constexpr int P = DP / KPL, M = KPL / 4, tok_floats = rec_arrays(RULE) * DP, Q = DP / 4;
   float o[REC_GROUP];
 #pragma unroll
   for (int tt = 0; tt < REC_GROUP; ++tt) {
@@ -302,6 +336,19 @@ __device__ __forceinline__ void rec_group(float (&s)[KPL], const float* __restri
           s[4 * m + 1] = fmaf(d.y, s[4 * m + 1], fmaf(-au.y, us, k.y * vj));
           s[4 * m + 2] = fmaf(d.z, s[4 * m + 2], fmaf(-au.z, us, k.z * vj));
           s[4 * m + 3] = fmaf(d.w, s[4 * m + 3], fmaf(-au.w, us, k.w * vj));
+          o0 = fmaf(s[4 * m], q.x, o0);
+          o1 = fmaf(s[4 * m + 1], q.y, o1);
+          o2 = fmaf(s[4 * m + 2], q.z, o2);
+          o3 = fmaf(s[4 * m + 3], q.w, o3);
+        }
+      } else if (GATED) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const float4 q = a[P * m], k = a[Q + P * m], d = a[2 * Q + P * m];
+          s[4 * m] = fmaf(d.x, s[4 * m], k.x * vj);
+          s[4 * m + 1] = fmaf(d.y, s[4 * m + 1], k.y * vj);
+          s[4 * m + 2] = fmaf(d.z, s[4 * m + 2], k.z * vj);
+          s[4 * m + 3] = fmaf(d.w, s[4 * m + 3], k.w * vj);
           o0 = fmaf(s[4 * m], q.x, o0);
           o1 = fmaf(s[4 * m + 1], q.y, o1);
           o2 = fmaf(s[4 * m + 2], q.z, o2);
@@ -349,14 +396,14 @@ __device__ __forceinline__ void rec_group(float (&s)[KPL], const float* __restri
 // otherwise stand idle. DP: the keys a head, filled up to a power of two (16 at least); sizes known to the compiler keep
 // the loop free of address arithmetic.
 constexpr int REC_STAGES = 3;
-template <bool DELTA, int KPL, int DP>
+template <int RULE, int KPL, int DP>
 __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kernel(
     const float* __restrict__ prep, const float* __restrict__ vsrc, long long ld_v, int v_col, const float* __restrict__ head_decay,
     float* __restrict__ state, long long slot_floats, const int* __restrict__ state_slot, const int* __restrict__ row_start,
     float* __restrict__ y, long long rows, int H, int D, int VD, int cols_per_block, int TC, int write_state) {
   constexpr int STAGES = REC_STAGES, P = DP / KPL, Dp = DP;
   extern __shared__ __align__(16) float sm[];
-  constexpr int NARR = DELTA ? 5 : 2;
+  constexpr int NARR = rec_arrays(RULE);
   constexpr int M = KPL / 4, tok_floats = NARR * Dp;
   const int stage_floats = TC * tok_floats + REC_CHUNK * cols_per_block;
   const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols_per_block;
@@ -367,7 +414,7 @@ __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kerne
   const int r0 = row_start[b], r1 = row_start[b + 1];
   if (r1 <= r0) return;
   float* S = state + (long long)state_slot[b] * slot_floats + (long long)h * D * VD;
-  const float c_h = DELTA ? 0.f : head_decay[h];
+  const float c_h = RULE != RULE_FIXED ? 0.f : head_decay[h];
   const int n_chunks = (r1 - r0 + TC - 1) / TC;
 
   // (the producer's lanes only)
@@ -421,8 +468,8 @@ __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kerne
       float* yg = y + (long long)t0 * ldy + (long long)h * VD + j;
       int g = 0;
       for (; g + REC_GROUP <= nt; g += REC_GROUP)
-        rec_group<DELTA, KPL, DP, true>(s, tok + g * tok_floats, vcol + g, yg + g * ldy, ldy, REC_GROUP, part, owns, c_h);
-      if (g < nt) rec_group<DELTA, KPL, DP, false>(s, tok + g * tok_floats, vcol + g, yg + g * ldy, ldy, nt - g, part, owns, c_h);
+        rec_group<RULE, KPL, DP, true>(s, tok + g * tok_floats, vcol + g, yg + g * ldy, ldy, REC_GROUP, part, owns, c_h);
+      if (g < nt) rec_group<RULE, KPL, DP, false>(s, tok + g * tok_floats, vcol + g, yg + g * ldy, ldy, nt - g, part, owns, c_h);
     }
     __syncthreads();
   }
@@ -437,11 +484,12 @@ __global__ void __launch_bounds__(REC_THREADS + 32) recurrence_scan_staged_kerne
   }
 }
 
-// grid (rows, groups): out[r, c] = y[r, c] / sqrt(mean over the group of y^2 + eps) * weight[c] * sigmoid(gate[r, c]) * scale
+// grid (rows, groups): out[r, c] = y[r, c] / sqrt(mean over the group of y^2 + eps) * weight[c] * act(gate[r, c]) * scale, act the
+// sigmoid or (silu_gate) g sigmoid(g); with shared_weight the weight has one group's entries, which every group uses
 template <typename T, typename G>
 __global__ void group_norm_gate_kernel(const float* __restrict__ y, const G* __restrict__ gate, long long ld_gate,
                                        const float* __restrict__ weight, float eps, float scale, T* __restrict__ out,
-                                       long long ld_out, int width, int group) {
+                                       long long ld_out, int width, int group, int silu_gate, int shared_weight) {
   __shared__ float red[33];
   const int r = blockIdx.x, c0 = blockIdx.y * group;
   const float* yr = y + (long long)r * width + c0;
@@ -451,7 +499,8 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ y, const G* __r
   const float inv = 1.f / sqrtf(ss / (float)group + eps);
   for (int i = threadIdx.x; i < group; i += blockDim.x) {
     const float g = to_f32(gate[(long long)r * ld_gate + c0 + i]);
-    out[(long long)r * ld_out + c0 + i] = from_f32<T>(yr[i] * inv * weight[c0 + i] * (1.f / (1.f + expf(-g))) * scale);
+    const float a = silu_gate ? g / (1.f + expf(-g)) : 1.f / (1.f + expf(-g));
+    out[(long long)r * ld_out + c0 + i] = from_f32<T>(yr[i] * inv * weight[(shared_weight ? 0 : c0) + i] * a * scale);
   }
 }
 
@@ -474,10 +523,11 @@ static void recurrence_block(int requests, int H, int VD, int P, long long want_
 }
 
 // floats of scratch the staged form wants for `rows` rows: the prepared tokens, then (fixed decays) the activated values
-extern "C" long long tl_recurrence_scratch_floats(long long rows, int H, int D, int VD, int delta) {
+// (rule: 0 a fixed decay a head, 1 the delta rule, 2 a decay a key channel and token)
+extern "C" long long tl_recurrence_scratch_floats(long long rows, int H, int D, int VD, int rule) {
   int P = 1;
   while (16 * P < D) P <<= 1;
-  return rows * H * ((delta ? 5 : 2) * 16LL * P + (delta ? 0 : VD));
+  return rows * H * (rec_arrays(rule) * 16LL * P + (rule == RULE_FIXED ? VD : 0));
 }
 
 // scratch: null runs the one-kernel form (steps of a few rows a request); else tl_recurrence_scratch_floats(rows, ...) floats.
@@ -485,12 +535,13 @@ extern "C" int tl_recurrence_scan(const float* proj, long long ld, int q_col, in
                                   long long ld_w, const float* w0, const float* a_bias, const float* head_decay, float rate,
                                   float key_eps, int silu_inputs, float* state, long long slot_floats, const int* state_slot,
                                   const int* row_start, int requests, float* y, int H, int D, int VD, int write_state,
-                                  float* scratch, long long rows, int sm_count, cudaStream_t stream) {
+                                  float* scratch, long long rows, int sm_count, int rule, float q_scale, cudaStream_t stream) {
   if (requests == 0) return 0;
-  const bool delta = wl != nullptr;
+  TL_REQUIRE(rule >= RULE_FIXED && rule <= RULE_GATED, "recurrence_scan: rule %d is not one of 0..2", rule);
+  const bool delta = rule == RULE_DELTA, fixed = rule == RULE_FIXED;
   TL_REQUIRE(H > 0 && D >= 1 && D <= 512 && VD >= 1, "recurrence_scan: %d heads, %d keys (up to 512), %d values", H, D, VD);
-  TL_REQUIRE(delta ? (w0 && a_bias && a_col >= 0) : head_decay != nullptr,
-             "recurrence_scan: the delta rule wants w, w0, a and its bias; the fixed decay wants a number a head");
+  TL_REQUIRE(delta ? (wl && w0 && a_bias && a_col >= 0) : (fixed ? head_decay != nullptr : (wl && w0)),
+             "recurrence_scan: the delta rule wants w, w0, a and its bias; the gated rule w and w0; the fixed decay a number a head");
   TL_REQUIRE(H <= 65535, "recurrence_scan: %d heads exceed the grid limit", H);
   int P = 1;
   while (16 * P < D) P <<= 1;
@@ -507,27 +558,28 @@ extern "C" int tl_recurrence_scan(const float* proj, long long ld, int q_col, in
   const int tiles = ceil_div(VD, cols_per_block);
   TL_REQUIRE(tiles <= 65535, "recurrence_scan: %d tiles of value columns exceed the grid limit", tiles);
   dim3 grid(requests, H, tiles);
-  const int narr = delta ? 5 : 2, Dp = 16 * P16;
+  const int narr = rec_arrays(rule), Dp = 16 * P16;
   if (scratch) {
     const long long pairs = rows * H;
     float* prep = scratch;
-    float* vact = delta ? nullptr : scratch + pairs * narr * Dp;
+    float* vact = fixed ? scratch + pairs * narr * Dp : nullptr;
     const unsigned pblocks = (unsigned)((pairs + 3) / 4);
-    if (delta)
-      recurrence_prepare_kernel<true><<<pblocks, 128, 0, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias, rate,
-                                                                   key_eps, silu_inputs, prep, vact, H, D, VD, Dp, pairs);
-    else
-      recurrence_prepare_kernel<false><<<pblocks, 128, 0, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias, rate,
-                                                                    key_eps, silu_inputs, prep, vact, H, D, VD, Dp, pairs);
+#define TL_RPREP(RULE_)                                                                                                          \
+  recurrence_prepare_kernel<RULE_><<<pblocks, 128, 0, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias, rate, \
+                                                                key_eps, silu_inputs, q_scale, prep, vact, H, D, VD, Dp, pairs)
+    if (delta) TL_RPREP(RULE_DELTA);
+    else if (fixed) TL_RPREP(RULE_FIXED);
+    else TL_RPREP(RULE_GATED);
+#undef TL_RPREP
     TL_LAUNCH_CHECK();
     // tokens a stage: as many (16 at most) as 96 KB hold in three stages
     int TC = REC_CHUNK;
     auto bytes = [&](int tc) { return (size_t)REC_STAGES * (tc * narr * Dp + REC_CHUNK * cols_per_block) * sizeof(float); };
     while (TC > 1 && bytes(TC) > 96 * 1024) TC >>= 1;
     const size_t smem = bytes(TC);
-    const float* vsrc = delta ? proj : vact;
-    const long long ld_v = delta ? ld : (long long)H * VD;
-    const int vc = delta ? v_col : 0;
+    const float* vsrc = fixed ? vact : proj;
+    const long long ld_v = fixed ? (long long)H * VD : ld;
+    const int vc = fixed ? 0 : v_col;
 #define TL_RSS(DELTA_, KPL_, DP_)                                                                                               \
   do {                                                                                                                          \
     if (smem > 48 * 1024)                                                                                                       \
@@ -553,8 +605,9 @@ extern "C" int tl_recurrence_scan(const float* proj, long long ld, int q_col, in
       default: TL_RSS_D(DELTA_, 512); break;    \
     }                                           \
   } while (0)
-    if (delta) TL_RSS_ALL(true);
-    else TL_RSS_ALL(false);
+    if (delta) TL_RSS_ALL(RULE_DELTA);
+    else if (fixed) TL_RSS_ALL(RULE_FIXED);
+    else TL_RSS_ALL(RULE_GATED);
 #undef TL_RSS_ALL
 #undef TL_RSS_D
 #undef TL_RSS
@@ -562,26 +615,26 @@ extern "C" int tl_recurrence_scan(const float* proj, long long ld, int q_col, in
     return 0;
   }
   const size_t smem = (size_t)(narr * REC_TOKENS * Dp + REC_TOKENS * cols_per_block) * sizeof(float);
-  if (delta) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(recurrence_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    recurrence_scan_kernel<true><<<grid, threads, smem, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias,
-                                                                  head_decay, rate, key_eps, silu_inputs, state, slot_floats,
-                                                                  state_slot, row_start, y, H, D, VD, P, cols_per_block,
-                                                                  write_state);
-  } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(recurrence_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    recurrence_scan_kernel<false><<<grid, threads, smem, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias,
-                                                                   head_decay, rate, key_eps, silu_inputs, state, slot_floats,
-                                                                   state_slot, row_start, y, H, D, VD, P, cols_per_block,
-                                                                   write_state);
-  }
+#define TL_RSCAN(RULE_)                                                                                                        \
+  do {                                                                                                                         \
+    if (smem > 48 * 1024)                                                                                                      \
+      cudaFuncSetAttribute(recurrence_scan_kernel<RULE_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
+    recurrence_scan_kernel<RULE_><<<grid, threads, smem, stream>>>(proj, ld, q_col, k_col, v_col, a_col, wl, ld_w, w0, a_bias, \
+                                                                   head_decay, rate, key_eps, silu_inputs, q_scale, state,     \
+                                                                   slot_floats, state_slot, row_start, y, H, D, VD, P,         \
+                                                                   cols_per_block, write_state);                               \
+  } while (0)
+  if (delta) TL_RSCAN(RULE_DELTA);
+  else if (fixed) TL_RSCAN(RULE_FIXED);
+  else TL_RSCAN(RULE_GATED);
+#undef TL_RSCAN
   TL_LAUNCH_CHECK();
   return 0;
 }
 
 extern "C" int tl_group_norm_gate(const float* y, const void* gate, long long ld_gate, int gate_dtype, const float* weight,
                                   float eps, float scale, void* out, long long ld_out, int rows, int width, int groups,
-                                  int dtype, cudaStream_t stream) {
+                                  int dtype, int silu_gate, int shared_weight, cudaStream_t stream) {
   if (rows == 0) return 0;
   TL_REQUIRE(width > 0 && groups > 0 && width % groups == 0 && groups <= 65535, "group_norm_gate: rows of %d in %d parts", width,
              groups);
@@ -590,7 +643,7 @@ extern "C" int tl_group_norm_gate(const float* y, const void* gate, long long ld
   dim3 grid(rows, groups);
 #define TL_GNG(T_, G_)                                                                                                   \
   group_norm_gate_kernel<T_, G_><<<grid, threads, 0, stream>>>(y, (const G_*)gate, ld_gate, weight, eps, scale, (T_*)out, \
-                                                               ld_out, width, group)
+                                                               ld_out, width, group, silu_gate, shared_weight)
   if (dtype == TL_FP32) {
     if (gate_dtype == TL_FP32) TL_GNG(float, float);
     else TL_GNG(float, bf16);

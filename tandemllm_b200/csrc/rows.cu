@@ -20,10 +20,12 @@ extern "C" const char* tl_cuda_error_string(int code) { return cudaGetErrorStrin
 
 namespace tl {
 
-// residual[r, :] = float(table[token[r], :]) * scale
+// residual[r, :] = float(table[token[r], :]) * scale, written `copies` times, copy_stride floats apart (a model that carries
+// several streams starts them all from the embedded row)
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                                  float* __restrict__ residual, int hidden, int vocab, int* __restrict__ status, float scale) {
+                                  float* __restrict__ residual, int hidden, int vocab, int* __restrict__ status, float scale,
+                                  int copies, long long copy_stride) {
   chain_next();
   chain_wait();
   const int r = blockIdx.x;
@@ -34,7 +36,10 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
   }
   const T* src = table + (size_t)tok * hidden;
   float* dst = residual + (size_t)r * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]) * scale;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = to_f32(src[c]) * scale;
+    for (int s = 0; s < copies; ++s) dst[(long long)s * copy_stride + c] = v;
+  }
 }
 
 // What is added to the residual before the norm. The previous branch's output comes in one of three forms, so
@@ -72,7 +77,70 @@ struct NormParams {
   int rows_per_block, out_rows;
   unsigned zero;             // 0 (see router_logits_one_row)
   int split;                 // CTAs a row (a cluster; one row a block with a router): each takes every split-th expert
+  // Several residual streams (hyper-connections): `residual` is [streams][rows][hidden], stream_stride floats apart. What
+  // is added is a sublayer's output y; with hc_mix the streams are first rewritten, all at once from the old ones,
+  // x_t <- sum_s hc_mix[s, t] x_s + hc_out[t] y, and the row that is normed is sum_t hc_in[t] x_t (hc_in null: the plain sum).
+  int streams;               // 0: one stream, the plain residual add
+  long long stream_stride;
+  const float* hc_mix;       // [streams, streams], indexed [from, to]; null: the streams stay as they are (nothing is added)
+  const float* hc_out;       // [streams]
+  const float* hc_in;        // [streams] or null
 };
+
+constexpr int MAX_STREAMS = 8;
+
+// One 16-byte piece (or, with N = 1, one number) of a row across all streams: rewrites the streams from y and returns what the
+// norm reads. Every sum runs over the streams in ascending order, the sublayer's output last.
+template <typename V>
+__device__ __forceinline__ V hyper_streams(const NormParams& p, size_t r, int c, V y, bool write) {
+  constexpr int N = sizeof(V) / sizeof(float);
+  const int S = p.streams;
+  float xs[MAX_STREAMS][N];
+#pragma unroll
+  for (int s = 0; s < MAX_STREAMS; ++s)
+    if (s < S) {
+      const V v = reinterpret_cast<const V*>(p.residual + (long long)s * p.stream_stride + r * p.hidden)[c];
+#pragma unroll
+      for (int i = 0; i < N; ++i) xs[s][i] = reinterpret_cast<const float*>(&v)[i];
+    }
+  float u[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) u[i] = 0.f;
+#pragma unroll
+  for (int t = 0; t < MAX_STREAMS; ++t)
+    if (t < S) {
+      float nt[N];
+      if (p.hc_mix) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) nt[i] = 0.f;
+#pragma unroll
+        for (int s = 0; s < MAX_STREAMS; ++s)
+          if (s < S) {
+            const float m = p.hc_mix[s * S + t];
+#pragma unroll
+            for (int i = 0; i < N; ++i) nt[i] = fmaf(m, xs[s][i], nt[i]);
+          }
+        const float o = p.hc_out[t];
+        V out;
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          nt[i] = fmaf(o, reinterpret_cast<const float*>(&y)[i], nt[i]);
+          reinterpret_cast<float*>(&out)[i] = nt[i];
+        }
+        if (write) reinterpret_cast<V*>(p.residual + (long long)t * p.stream_stride + r * p.hidden)[c] = out;
+      } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) nt[i] = xs[t][i];
+      }
+      const float w = p.hc_in ? p.hc_in[t] : 1.f;
+#pragma unroll
+      for (int i = 0; i < N; ++i) u[i] = fmaf(w, nt[i], u[i]);
+    }
+  V ret;
+#pragma unroll
+  for (int i = 0; i < N; ++i) reinterpret_cast<float*>(&ret)[i] = u[i];
+  return ret;
+}
 
 // With a router and many rows, a block norms this many rows before it multiplies them by the router's weights,
 // so that the weights are read once per block and not once per row.
@@ -272,13 +340,15 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
     __syncthreads();
   }
   float* res = p.residual + (size_t)r * hidden;
-  const bool adds = p.delta || p.expert_rows;
+  const bool hyper = p.streams > 0;              // several streams: what is added rewrites them, and their weighed sum is normed
+  const bool adds = !hyper && (p.delta || p.expert_rows);
+  const bool hyper_writes = hyper && !p.gather && rank == 0;
   const bool vec = (hidden & 3) == 0;           // rows are then 16-byte aligned: four elements a step
   float ss = 0.f;
   // A row that gets a plain tensor added (or nothing) and whose thread holds at most IN_REGS 16-byte pieces of it: all
   // of the thread's loads are sent before the first is used, and the pieces stay in registers until they are normed.
   constexpr int IN_REGS = 4;
-  const bool in_regs = vec && !p.expert_rows && (hidden >> 2) <= G * IN_REGS;
+  const bool in_regs = vec && !hyper && !p.expert_rows && (hidden >> 2) <= G * IN_REGS;
   float4 xr[IN_REGS];
   if (in_regs) {
     const int h4 = hidden >> 2;
@@ -316,7 +386,7 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
       const int h4 = hidden >> 2;
       const float4* res4 = reinterpret_cast<const float4*>(res);
       for (int c = t; c < h4; c += G) {
-        float4 x = res4[c];
+        float4 x = hyper ? make_float4(0.f, 0.f, 0.f, 0.f) : res4[c];       // (several streams: x is first the sublayer's output)
         if (p.delta) {
           float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
           for (int s = 0; s < p.parts; ++s) {
@@ -358,12 +428,13 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
           }
           x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
         }
+        if (hyper) x = hyper_streams<float4>(p, (size_t)r, c, x, hyper_writes);
         reinterpret_cast<float4*>(row)[c] = x;
         ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
       }
     } else {
       for (int c = t; c < hidden; c += G) {
-        float x = res[c];
+        float x = hyper ? 0.f : res[c];
         if (p.delta) {
           float d = 0.f;
           for (int s = 0; s < p.parts; ++s) d += p.delta[(long long)s * p.part_stride + (size_t)r * hidden + c];
@@ -379,6 +450,7 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
           }
           x += d;
         }
+        if (hyper) x = hyper_streams<float>(p, (size_t)r, c, x, hyper_writes);
         row[c] = x;
         ss += x * x;
       }
@@ -477,19 +549,25 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 
 using namespace tl;
 
-extern "C" int tl_embed_rows(const void* table, const int* tokens, float* residual, int rows, int hidden, int vocab,
-                             int dtype, int* status, float scale, cudaStream_t stream) {
+extern "C" int tl_embed_rows_copies(const void* table, const int* tokens, float* residual, int rows, int hidden, int vocab,
+                                    int dtype, int* status, float scale, int copies, long long copy_stride, cudaStream_t stream) {
   if (rows == 0) return 0;
-  TL_REQUIRE(rows > 0 && hidden > 0 && vocab > 0, "embed_rows: rows %d hidden %d vocab %d", rows, hidden, vocab);
+  TL_REQUIRE(rows > 0 && hidden > 0 && vocab > 0 && copies >= 1, "embed_rows: rows %d hidden %d vocab %d copies %d", rows, hidden,
+             vocab, copies);
   const int threads = hidden >= 1024 ? 256 : 128;
   cudaError_t e;
   if (dtype == TL_FP32)
     e = launch_chained(embed_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, (const float*)table, tokens, residual,
-                       hidden, vocab, status, scale);
+                       hidden, vocab, status, scale, copies, copy_stride);
   else
     e = launch_chained(embed_rows_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, (const bf16*)table, tokens, residual,
-                       hidden, vocab, status, scale);
+                       hidden, vocab, status, scale, copies, copy_stride);
   return (int)e;
+}
+
+extern "C" int tl_embed_rows(const void* table, const int* tokens, float* residual, int rows, int hidden, int vocab,
+                             int dtype, int* status, float scale, cudaStream_t stream) {
+  return tl_embed_rows_copies(table, tokens, residual, rows, hidden, vocab, dtype, status, scale, 1, 0, stream);
 }
 
 extern "C" void tl_set_chained_launches(int enabled) { chained_launches() = enabled; }
@@ -514,6 +592,16 @@ static cudaError_t launch_clustered(void (*kernel)(KernelArgs...), dim3 grid, di
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// The same over `streams` residual streams (see NormParams); streams 0 is the plain residual add.
+extern "C" int tl_add_rmsnorm_streams(float* residual, const float* delta, int parts, long long part_stride,
+                              const float* expert_rows, int expert_parts, long long expert_part_stride,
+                              const int* pos_of_pair, const int* ids, const float* wts, int top_k,
+                              const float* weight, void* normed, float* normed32, const int* gather, int out_rows,
+                              int hidden, float eps, int dtype, const float* router_w, const float* router_bias, int E,
+                              int route_k, int normalize, float floor_, float scale, int* route_ids, float* route_wts,
+                              int streams, long long stream_stride, const float* hc_mix, const float* hc_out, const float* hc_in,
+                              cudaStream_t stream);
+
 extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, long long part_stride,
                               const float* expert_rows, int expert_parts, long long expert_part_stride,
                               const int* pos_of_pair, const int* ids, const float* wts, int top_k,
@@ -521,7 +609,25 @@ extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, lo
                               int hidden, float eps, int dtype, const float* router_w, const float* router_bias, int E,
                               int route_k, int normalize, float floor_, float scale, int* route_ids, float* route_wts,
                               cudaStream_t stream) {
+  return tl_add_rmsnorm_streams(residual, delta, parts, part_stride, expert_rows, expert_parts, expert_part_stride, pos_of_pair,
+                                ids, wts, top_k, weight, normed, normed32, gather, out_rows, hidden, eps, dtype, router_w,
+                                router_bias, E, route_k, normalize, floor_, scale, route_ids, route_wts, 0, 0, nullptr, nullptr,
+                                nullptr, stream);
+}
+
+extern "C" int tl_add_rmsnorm_streams(float* residual, const float* delta, int parts, long long part_stride,
+                              const float* expert_rows, int expert_parts, long long expert_part_stride,
+                              const int* pos_of_pair, const int* ids, const float* wts, int top_k,
+                              const float* weight, void* normed, float* normed32, const int* gather, int out_rows,
+                              int hidden, float eps, int dtype, const float* router_w, const float* router_bias, int E,
+                              int route_k, int normalize, float floor_, float scale, int* route_ids, float* route_wts,
+                              int streams, long long stream_stride, const float* hc_mix, const float* hc_out, const float* hc_in,
+                              cudaStream_t stream) {
   if (out_rows == 0) return 0;
+  TL_REQUIRE(streams >= 0 && streams <= MAX_STREAMS, "add_rmsnorm: %d residual streams; up to %d are implemented", streams,
+             MAX_STREAMS);
+  TL_REQUIRE(streams == 0 || ((hc_mix != nullptr) == (hc_out != nullptr) && (hc_mix || (!delta && !expert_rows))),
+             "add_rmsnorm: what is added to %d streams needs their mixing matrix and their output weights", streams);
   TL_REQUIRE(out_rows > 0 && hidden > 0, "add_rmsnorm: rows %d hidden %d", out_rows, hidden);
   TL_REQUIRE(!delta || parts >= 1, "add_rmsnorm: %d parts", parts);
   TL_REQUIRE(!expert_rows || (top_k > 0 && top_k <= MAX_TOP_K && pos_of_pair && ids && wts),
@@ -551,6 +657,7 @@ p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = exp
   p.router_bias = router_bias; p.E = E; p.route_k = route_k; p.normalize = normalize; p.floor_ = floor_; p.scale = scale;
   p.route_ids = route_ids; p.route_wts = route_wts;
   p.rows_per_block = rows_per_block; p.out_rows = out_rows; p.zero = 0u;
+  p.streams = streams; p.stream_stride = stream_stride; p.hc_mix = hc_mix; p.hc_out = hc_out; p.hc_in = hc_in;
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (threads < 32 * rows_per_block) threads = 32 * rows_per_block;       // whole warps a row
   // A decode step's router: one block a row would pull all of the router's weights through one SM (256 KB for 32
@@ -560,7 +667,8 @@ p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = exp
   // that all CTAs still run at once, one an SM (37 rows x 4, 74 rows x 2: 8119 -> 8246 tok/s at batch 32, 13.2 k -> 13.5 k
   // at batch 64).
   p.split = 1;
-  if (rows_per_block == 1 && router_w && E >= 16 && (hidden & 3) == 0)
+  // (not over several streams: the row's first CTA would rewrite them while the others still read them)
+  if (rows_per_block == 1 && router_w && E >= 16 && (hidden & 3) == 0 && streams == 0)
     p.split = out_rows <= ROUTER_SPLIT_ROWS ? ROUTER_SPLIT : (out_rows <= 37 ? 4 : (out_rows <= 74 ? 2 : 1));
   const dim3 grid(ceil_div(out_rows, rows_per_block) * p.split);
   const int per = !router_w ? 0 : (E <= 32 ? 1 : (E <= 128 ? 4 : MAX_EXPERTS / 32));

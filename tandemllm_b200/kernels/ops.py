@@ -18,7 +18,7 @@ FP32, BF16 = 0, 1
 TL_BAD_ARGUMENT = 100001
 # the gate activations of gated products (TL_ACT_* of csrc/common.cuh) and the router's scoring functions (TL_SCORE_*
 # of csrc/route.cuh), by the names a part's spec gives them
-ACTIVATIONS = {"silu": 1, "gelu": 2, "relu2": 3, "identity": 4, "xielu": 5, "clamped_swish": 6, "softcap": 7, "tanh": 8}
+ACTIVATIONS = {"silu": 1, "gelu": 2, "relu2": 3, "identity": 4, "xielu": 5, "clamped_swish": 6, "softcap": 7, "tanh": 8, "scale": 9}
 SCORINGS = {"sigmoid": 0, "softmax": 1}
 
 
@@ -63,6 +63,12 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 _SIGNATURES = {
     "tl_embed_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p],
+    "tl_embed_rows_copies": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_int, c_longlong,
+                             c_void_p],
+    "tl_add_rmsnorm_streams": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p,
+                               c_int, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_float, c_float, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p],
     "tl_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                        c_void_p,
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -120,23 +126,23 @@ _SIGNATURES = {
                           c_void_p],
     "tl_rmsnorm_rows": [c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
     "tl_head_linear": [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_int,
-                       c_int, c_int, c_void_p],
+                       c_int, c_int, c_void_p, c_longlong, c_void_p],
     "tl_attention_latent": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p,
-                            c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                            c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "tl_add_layernorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                          c_int, c_void_p],
     "tl_qkv_rotate_store": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_void_p, c_void_p],
+                            c_void_p, c_float, c_void_p, c_longlong, c_void_p, c_void_p],
     "tl_attention_flex": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float,
                           c_int, c_int, c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_longlong, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_void_p, c_void_p],
     "tl_recurrence_scan": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                            c_float, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-                           c_int, c_int, c_void_p, c_longlong, c_int, c_void_p],
+                           c_int, c_int, c_void_p, c_longlong, c_int, c_int, c_float, c_void_p],
     "tl_recurrence_scratch_floats": [c_longlong, c_int, c_int, c_int, c_int],
     "tl_group_norm_gate": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_float, c_float, c_void_p, c_longlong, c_int,
-                           c_int, c_int, c_int, c_void_p],
+                           c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tl_set_gate_constants": [c_float, c_float],
     "tl_graph_capture_begin": [c_void_p],
     "tl_graph_capture_end": [c_void_p, c_void_p, c_void_p],
@@ -215,11 +221,14 @@ def _need(t: torch.Tensor, dtype: torch.dtype | None, name: str) -> None:
 # ------------------------------------------------------------------------------------------ rows
 def embed_rows(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor, status: torch.Tensor,
                scale: float = 1.0) -> None:
-    """residual[r] = table[tokens[r]] * scale in 32-bit."""
+    """residual[r] = table[tokens[r]] * scale in 32-bit; a residual of several streams [streams, rows, hidden] gets the row in
+    every stream."""
     _need(table, None, "embedding table"); _need(tokens, torch.int32, "tokens"); _need(residual, torch.float32, "residual")
-    rows, hidden = residual.shape
-    check(core().tl_embed_rows(ptr(table), ptr(tokens), ptr(residual), rows, hidden, table.shape[0],
-                               dtype_code(table.dtype), ptr(status), float(scale), stream()), "embed_rows")
+    copies = residual.shape[0] if residual.dim() == 3 else 1
+    rows, hidden = residual.shape[-2:]
+    check(core().tl_embed_rows_copies(ptr(table), ptr(tokens), ptr(residual), rows, hidden, table.shape[0],
+                                      dtype_code(table.dtype), ptr(status), float(scale), copies, rows * hidden, stream()),
+          "embed_rows")
 
 
 class PartialSums:
@@ -271,6 +280,20 @@ class GatedSum:
         return total if self.experts is None else total + self.experts.materialize()
 
 
+class StreamUpdate:
+    """What a sublayer leaves for a residual of several streams [streams, rows, hidden] (hyper-connections): its output `delta`
+    (None, a tensor or a deferred form) with the weights that take it into the streams, all streams at once from the old
+    ones, x_t <- sum_s mix[s, t] x_s + out[t] delta (`mix` float32 [streams, streams], `out` float32 [streams]; both None:
+    nothing is added yet), and the weights `read` (float32 [streams]; None: all one) with which the next norm sums the
+    streams into the row it norms. The norm kernel does all of it."""
+
+    def __init__(self, delta, mix: torch.Tensor | None, out: torch.Tensor | None, read: torch.Tensor | None = None):
+        self.delta, self.mix, self.out, self.read = delta, mix, out, read
+
+    def reading(self, read: torch.Tensor | None) -> "StreamUpdate":
+        return StreamUpdate(self.delta, self.mix, self.out, read)
+
+
 def materialize(branch):
     """A branch output as a plain tensor, whatever form a part returned it in."""
     return branch.materialize() if isinstance(branch, (PartialSums, ExpertRows, GatedSum)) else branch
@@ -283,10 +306,22 @@ def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float,
     `PartialSums` or an `ExpertRows`. With `gather` (int32 row indices) the output row i is computed from row
     gather[i] and the residual is left unchanged. `out32` also receives the normalised rows unrounded. `route`
     (router weights float32 [E, hidden], bias, k, normalize, scoring, floor, scale, ids, wts) also runs the router on the
-    unrounded rows and fills ids int32 [rows, k] and wts float32 [rows, k]."""
+    unrounded rows and fills ids int32 [rows, k] and wts float32 [rows, k]. A residual of several streams [streams, rows,
+    hidden] takes a `StreamUpdate`: its delta rewrites the streams and their weighed sum is what is normed."""
     _need(residual, torch.float32, "residual"); _need(weight, torch.float32, "norm weight"); _need(out, None, "normed")
     if out32 is not None:
         _need(out32, torch.float32, "normed32")
+    streams, hc = 0, None
+    if isinstance(delta, StreamUpdate):
+        hc, delta = delta, delta.delta
+        if residual.dim() != 3 or (hc.mix is not None and tuple(hc.mix.shape) != (residual.shape[0],) * 2):
+            raise KernelError(f"a stream update for a residual of shape {tuple(residual.shape)}")
+        for t in (hc.mix, hc.out, hc.read):
+            if t is not None:
+                _need(t, torch.float32, "stream weights")
+        streams = residual.shape[0]
+    elif residual.dim() != 2:
+        raise KernelError(f"a residual of shape {tuple(residual.shape)} without a stream update")
     dense = parts = stride = 0
     rows_ptr = pos = ids = wts = None
     top_k, eparts, estride = 0, 1, 0
@@ -305,14 +340,15 @@ def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float,
     r = route or {}
     if route:
         _need(r["weight"], torch.float32, "router weight"); _need(r["ids"], torch.int32, "ids"); _need(r["wts"], torch.float32, "wts")
-    check(core().tl_add_rmsnorm(
+    check(core().tl_add_rmsnorm_streams(
         ptr(residual), dense or None, parts, stride, ptr(rows_ptr), eparts, estride, ptr(pos), ptr(ids), ptr(wts), top_k,
         ptr(weight),
         ptr(out), ptr(out32), ptr(gather), n_out, hidden, float(eps), dtype_code(out.dtype), ptr(r.get("weight")),
         ptr(r.get("bias")), r["weight"].shape[0] if route else 0, int(r.get("k", 0)),
         route_flags(r.get("normalize", 0), r.get("scoring", "sigmoid"), r.get("groups")),
-        float(r.get("floor", 0.0)), float(r.get("scale", 1.0)), ptr(r.get("ids")), ptr(r.get("wts")), stream()),
-        "add_rmsnorm")
+        float(r.get("floor", 0.0)), float(r.get("scale", 1.0)), ptr(r.get("ids")), ptr(r.get("wts")),
+        streams, residual.stride(0) if streams else 0, ptr(hc.mix) if hc else None, ptr(hc.out) if hc else None,
+        ptr(hc.read) if hc else None, stream()), "add_rmsnorm")
     return out
 
 
@@ -524,23 +560,29 @@ def rmsnorm_rows(x: torch.Tensor, n: int, weight: torch.Tensor, eps: float, out:
 
 
 def head_linear(a: torch.Tensor, ld_a: int, a_head: int, w: torch.Tensor, out: torch.Tensor, ld_out: int, out_head: int,
-                rows: int) -> torch.Tensor:
+                rows: int, gate: torch.Tensor | None = None) -> torch.Tensor:
     """out[r, h, n] = sum_k a[r, h, k] w[h, n, k] with w [heads, N, K]; `a` and `out` addressed by a row stride and a head
-    stride (elements)."""
+    stride (elements). With `gate` (logits [rows, heads * N] of the operands' type, unit inner stride) the result is
+    multiplied entry by entry by sigmoid(gate)."""
     _need(w, a.dtype, "head weights")
     H, N, K = w.shape
+    if gate is not None and (gate.dtype != a.dtype or gate.stride(-1) != 1):
+        raise KernelError("head product: a gate of the operands' type with unit stride")
     check(core().tl_head_linear(ptr(a), int(ld_a), int(a_head), ptr(w), ptr(out), int(ld_out), int(out_head), rows, H, N, K,
-                                dtype_code(a.dtype), dtype_code(out.dtype), stream()), "head_linear")
+                                dtype_code(a.dtype), dtype_code(out.dtype), ptr(gate), gate.stride(0) if gate is not None else 0,
+                                stream()), "head_linear")
     return out
 
 
-def attention_latent(q, cache, table, page_size, req_of_row, positions, scale, window, out, latent: int, status) -> torch.Tensor:
-    """out[r, h, :latent] = softmax over the visible keys of scale * q[r, h] . key, applied to the keys' latent parts."""
+def attention_latent(q, cache, table, page_size, req_of_row, positions, scale, window, out, latent: int, status,
+                     sinks: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r, h, :latent] = softmax over the visible keys of scale * q[r, h] . key, applied to the keys' latent parts. With
+    `sinks` (float32 [heads]) a head's denominator also holds exp(sink), which has no key and no value."""
     _need(q, torch.float32, "q'"); _need(out, cache.dtype, "out")
     rows, H, Dk = q.shape
     check(core().tl_attention_latent(ptr(q), ptr(cache), ptr(table), table.shape[1], int(page_size), cache.shape[0],
                                      ptr(req_of_row), ptr(positions), float(scale), int(window or 0), ptr(out), rows, H, latent,
-                                     Dk, dtype_code(cache.dtype), ptr(status), stream()), "attention_latent")
+                                     Dk, dtype_code(cache.dtype), ptr(status), ptr(sinks), stream()), "attention_latent")
     return out
 
 
@@ -692,17 +734,24 @@ def attention_join(scratch, positions, window, out, n_spans: int, span_keys: int
 
 def qkv_rotate_store(qkv, q_col: int, k_col: int, v_col: int, inv_freq, rot: int, inv_freq_v, positions, req_of_row, table,
                      page_size: int, q_out, k_cache, v_cache, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
-                     status) -> None:
+                     status, rot_magnitude: float = 1.0, v_other=None, v_blend=None) -> None:
     """From the rows of one fused product (`q_col`, `k_col`, `v_col`: where each part begins in a row; `k_col` < 0: the rows
-    hold queries only): rotary over the first `rot` entries of every q and k head (halves layout; `inv_freq` None: none), the
-    values turned over all their entries by `inv_freq_v` (None: as projected); q to `q_out`, k and v into their pages."""
+    hold queries only): rotary over the first `rot` entries of every q and k head (halves layout; `inv_freq` None: none), its
+    sines and cosines times `rot_magnitude`; the values turned over all their entries by `inv_freq_v` (None: as projected), or
+    blended with the same rows of `v_other` (a view [rows, kv heads * value_dim] of the compute dtype, unit inner stride):
+    (1 - l) v + l v_other with l = `v_blend` (float32, one number on the device); q to `q_out`, k and v into their pages."""
     _need(qkv, None, "qkv"); _need(q_out, qkv.dtype, "q")
+    if v_other is not None and (v_other.dtype != qkv.dtype or v_other.stride(1) != 1 or
+                                v_other.shape != (qkv.shape[0], num_kv_heads * value_dim)):
+        raise KernelError(f"values to blend with of shape {tuple(v_other.shape)}, dtype {v_other.dtype}")
     check(core().tl_qkv_rotate_store(ptr(qkv), qkv.stride(0), int(q_col), int(k_col), int(v_col), ptr(inv_freq), int(rot),
                                      ptr(inv_freq_v), ptr(positions), ptr(req_of_row), ptr(table),
                                      table.shape[1] if table is not None else 0, int(page_size),
                                      k_cache.shape[0] if k_cache is not None else 0, ptr(q_out), ptr(k_cache), ptr(v_cache),
                                      qkv.shape[0], num_heads, num_kv_heads, head_dim, value_dim, dtype_code(qkv.dtype),
-                                     ptr(status), stream()), "qkv_rotate_store")
+                                     ptr(status), float(rot_magnitude), ptr(v_other),
+                                     v_other.stride(0) if v_other is not None else 0, ptr(v_blend), stream()),
+          "qkv_rotate_store")
 
 
 def attention_flex(q, k_cache, v_cache, table, page_size: int, req_of_row, positions, scale: float, softcap, window,
@@ -730,9 +779,10 @@ RECURRENCE_STAGED_ROWS = 8      # a request that brings more rows than this take
 def recurrence_scan(proj, q_col: int, k_col: int, v_col: int, state, state_slot, row_start, requests: int, y, heads: int,
                     key_dim: int, value_dim: int, *, head_decay=None, a_col: int = -1, w=None, w0=None, a_bias=None,
                     rate: float = 0.0, key_eps: float = 0.0, silu_inputs: bool = False, write_state: bool = True,
-                    max_rows: int = 1) -> torch.Tensor:
+                    max_rows: int = 1, q_scale: float = 1.0) -> torch.Tensor:
     """The recurrence over a matrix state a head (csrc/recurrence.cu): with `head_decay` (float32 [heads]) the decayed sum of
-    outer products, with `w` (float32 [rows, heads * key_dim], the decay's logits) the generalized delta rule. `proj`:
+    outer products, with `w` (float32 [rows, heads * key_dim], the decay's logits) and `a_col` the generalized delta rule,
+    with `w` alone the gated outer products (a decay sigmoid(w + w0)^rate a key channel). q is multiplied by `q_scale`. `proj`:
     float32 rows holding q, k, v (and the removal logits at `a_col`) at the given columns; `state` [slots, heads, key_dim,
     value_dim] float32; `y` [rows, heads * value_dim] float32. `max_rows`: the most rows a request brings; above
     RECURRENCE_STAGED_ROWS the tokens' activations, decays and unit keys are formed side by side first and the scan fetches
@@ -741,28 +791,32 @@ def recurrence_scan(proj, q_col: int, k_col: int, v_col: int, state, state_slot,
     if w is not None:
         _need(w, torch.float32, "decay logits")
     rows = proj.shape[0]
+    rule = 0 if w is None else (1 if a_col >= 0 else 2)
     scratch = None
     if max_rows > RECURRENCE_STAGED_ROWS:
-        scratch = torch.empty(core().tl_recurrence_scratch_floats(rows, heads, key_dim, value_dim, int(w is not None)),
+        scratch = torch.empty(core().tl_recurrence_scratch_floats(rows, heads, key_dim, value_dim, rule),
                               dtype=torch.float32, device=proj.device)
     check(core().tl_recurrence_scan(ptr(proj), proj.stride(0), int(q_col), int(k_col), int(v_col), int(a_col), ptr(w),
                                     w.stride(0) if w is not None else 0, ptr(w0), ptr(a_bias), ptr(head_decay), float(rate),
                                     float(key_eps), int(silu_inputs), ptr(state), state[0].numel(), ptr(state_slot),
                                     ptr(row_start), int(requests), ptr(y), heads, key_dim, value_dim, int(write_state),
-                                    ptr(scratch), rows, sm_count(), stream()), "recurrence_scan",
+                                    ptr(scratch), rows, sm_count(), rule, float(q_scale), stream()), "recurrence_scan",
           kernels=2 if scratch is not None else 1)
     return y
 
 
-def group_norm_gate(y, gate, ld_gate: int, weight, eps: float, groups: int, scale: float, out) -> torch.Tensor:
-    """out = y / rms(y) over each of `groups` equal parts of a row, times `weight`, times sigmoid(gate), times `scale`. `gate`
-    begins at the first logit, rows `ld_gate` apart (32-bit or the compute dtype); `out` may be a column slice."""
+def group_norm_gate(y, gate, ld_gate: int, weight, eps: float, groups: int, scale: float, out, gate_activation: str = "sigmoid"
+                    ) -> torch.Tensor:
+    """out = y / rms(y) over each of `groups` equal parts of a row, times `weight`, times sigmoid(gate) (or, with
+    `gate_activation` "silu", gate sigmoid(gate)), times `scale`. `gate` begins at the first logit, rows `ld_gate` apart
+    (32-bit or the compute dtype); `out` may be a column slice. A weight of one part's size is shared by all parts."""
     _need(y, torch.float32, "y")
     rows, width = y.shape
     if out.stride(1) != 1 or out.shape != (rows, width):
         raise KernelError(f"group_norm_gate output of shape {tuple(out.shape)}")
     check(core().tl_group_norm_gate(ptr(y), ptr(gate), int(ld_gate), dtype_code(gate.dtype), ptr(weight), float(eps),
                                     float(scale), ptr(out), out.stride(0), rows, width, int(groups), dtype_code(out.dtype),
+                                    int(gate_activation == "silu"), int(weight.numel() * groups == width and groups > 1),
                                     stream()), "group_norm_gate")
     return out
 

@@ -85,10 +85,10 @@ def lib():
         l.tl_tc_last_error.restype = ctypes.c_char_p
         l.tl_attention_latent_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, ctypes.c_float,
                                               c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                              c_void_p, c_void_p]
+                                              c_void_p, c_void_p, c_void_p]
         l.tl_attention_latent_mma.restype = c_int
         l.tl_head_linear_mma.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int,
-                                         c_int, c_int, c_int, c_void_p]
+                                         c_int, c_int, c_int, c_void_p, c_longlong, c_void_p]
         l.tl_head_linear_mma.restype = c_int
         l.tl_attention_latent_mma_scratch.argtypes = [c_int, c_int, c_int, c_int]
         l.tl_attention_latent_mma_scratch.restype = c_longlong
@@ -325,7 +325,7 @@ class TensorCore:
             "attention_headmix_mma")
         return True
 
-    def attention_latent(self, q, cache, table, step, scale, window, out, latent: int, runtime) -> bool:
+    def attention_latent(self, q, cache, table, step, scale, window, out, latent: int, runtime, sinks=None) -> bool:
         """Latent attention on the tensor cores (csrc/attention_latent_mma.cu): q float32 [rows, heads, latent + rotated part],
         out bfloat16 [rows, heads, latent]. Steps of few rows and long contexts are cut into spans of keys, a CTA each, so
         that the GPU is filled; False when the cache is not bfloat16."""
@@ -350,18 +350,23 @@ class TensorCore:
             q.data_ptr(), cache.k.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size, cache.k.shape[0],
             step.req_of_row.data_ptr(), step.row_start.data_ptr(), step.positions.data_ptr(), float(scale), int(window or 0),
             out.data_ptr(),
-            ops.ptr(scratch), R, step.n_requests, tiles, H, latent, Dk, n_spans, span, self.status.data_ptr(), ops.stream()),
+            ops.ptr(scratch), R, step.n_requests, tiles, H, latent, Dk, n_spans, span, self.status.data_ptr(), ops.ptr(sinks),
+            ops.stream()),
             "attention_latent_mma", kernels=2 if n_spans > 1 else 1)
         return True
 
-    def head_linear(self, a, ld_a: int, a_head: int, w, out, ld_out: int, out_head: int, rows: int) -> bool:
+    def head_linear(self, a, ld_a: int, a_head: int, w, out, ld_out: int, out_head: int, rows: int, gate=None) -> bool:
         """out[r, h, n] = sum_k a[r, h, k] w[h, n, k] on the tensor cores (csrc/head_linear_mma.cu) for bfloat16 operands
-        (out bfloat16 or float32); False for anything else."""
+        (out bfloat16 or float32), times sigmoid(gate[r, h, n]) with `gate` (bfloat16 logits, unit inner stride); False for
+        anything else."""
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
+            return False
+        if gate is not None and (gate.dtype != torch.bfloat16 or gate.stride(-1) != 1):
             return False
         H, N, K = w.shape
         _check(lib().tl_head_linear_mma(a.data_ptr(), int(ld_a), int(a_head), w.data_ptr(), out.data_ptr(), int(ld_out),
-                                        int(out_head), rows, H, N, K, ops.dtype_code(out.dtype), ops.stream()), "head_linear_mma")
+                                        int(out_head), rows, H, N, K, ops.dtype_code(out.dtype), ops.ptr(gate),
+                                        gate.stride(0) if gate is not None else 0, ops.stream()), "head_linear_mma")
         return True
 
     def in_proj_conv(self, x, w_in, b_in, taps, b_taps, state, state_slot, req_of_row, positions, y,

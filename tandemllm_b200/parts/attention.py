@@ -19,7 +19,14 @@ Options, each a parameter of the spec so that another design can name its own co
               j base^(-2m / value_dim)) and cached so; a head's output at position i is turned back by -i before any gate;
   `entry_gate`: the name of a matrix [Hq * value_dim, hidden]: the concatenated heads times sigmoid(gate n) entry by entry;
   `borrows_keys`: the layer has no k and v matrices: its site reads the cache of the site its run order names;
-  `cache_window`, `cache_keep_first`: what the pages must keep readable when other sites read them through wider masks.
+  `cache_window`, `cache_keep_first`: what the pages must keep readable when other sites read them through wider masks;
+  `bias`: q, k, v and the out projection have biases (`<matrix's name without the weight suffix><bias_suffix>`, ".b" by
+              default), added in the products;
+  `value_carry` {key, blend}: values carried from layer to layer within a step. The first layer of a step that names `key`
+              leaves its values as projected (`blend` None there); a later layer with the same `key` caches and attends over
+              (1 - l) v + l v_first, l the one number stored as `<prefix><blend>`, v_first the first layer's values of the same
+              row. Both must have the same number of KV heads and value size.
+A position encoding whose sines and cosines carry a factor (`magnitude`) passes it to the q/k kernel.
 Any of these takes the mixer to the kernels of csrc/attention_flex.cu, which have all of them as arguments.
 
 Every size (heads, KV heads, head size), the scale, the window and the names of its tensors are
@@ -53,7 +60,8 @@ class AttentionMixer(Part):
         if spec.get("head_mix") or spec.get("gate"):
             if not 1 <= self.head_dim <= 256:       # the head-mixing kernels take any head size the q/k kernel does
                 raise ValueError(f"head size {self.head_dim}: 1 to 256 are implemented")
-        elif any(spec.get(k) for k in ("softcap", "keep_first", "value_rotation", "entry_gate", "borrows_keys")) or \
+        elif any(spec.get(k) for k in ("softcap", "keep_first", "value_rotation", "entry_gate", "borrows_keys", "bias",
+                                       "value_carry")) or \
                 int(spec.get("value_dim") or self.head_dim) != self.head_dim:
             if not (1 <= self.head_dim <= 256 and 1 <= int(spec.get("value_dim") or self.head_dim) <= 256):
                 raise ValueError(f"head sizes {self.head_dim} and {spec.get('value_dim')}: 1 to 256 are implemented")
@@ -85,15 +93,22 @@ class AttentionMixer(Part):
         self.borrows_keys = bool(spec.get("borrows_keys", False))
         self.cache_window = spec.get("cache_window", self.window)
         self.cache_keep_first = int(spec.get("cache_keep_first", self.keep_first) or 0)
+        carry = spec.get("value_carry")
+        self.carry_key = str(carry["key"]) if carry else None
+        self.carry_blend_name = prefix + carry["blend"] if carry and carry.get("blend") else None
+        self.bias_suffix = str(spec.get("bias_suffix", ".b"))
         self.flex = bool(self.value_dim != self.head_dim or self.softcap or self.keep_first or self.value_rotation
-                         or self.entry_gate_name or self.borrows_keys)
+                         or self.entry_gate_name or self.borrows_keys or self.bias or carry
+                         or getattr(self.position, "magnitude", 1.0) != 1.0)
         if self.flex:
-            if self.head_mix_name or self.gate_name or self.q_norm or self.values != "projected" or self.bias:
+            if self.head_mix_name or self.gate_name or self.q_norm or self.values != "projected":
                 raise ValueError("capped scores, kept first tokens, turned values, an entry-wise gate and borrowed keys do "
                                  "not combine with mixed heads, a gate a head, q/k norms or values that are the keys")
             if self.value_rotation and self.value_dim % 2:
                 raise ValueError(f"values of odd size {self.value_dim} cannot be turned in pairs")
-        self.inv_freq_v = None
+            if carry and (self.value_rotation or self.borrows_keys):
+                raise ValueError("carried values are neither turned nor borrowed")
+        self.inv_freq_v = self.b_qkv = self.b_out = self.carry_blend = None
 
     @property
     def out_dim(self) -> int:
@@ -116,7 +131,14 @@ class AttentionMixer(Part):
                         TensorSpec(self.n["v"] + sfx, (self.num_kv_heads * self.value_dim, H))]
             if self.entry_gate_name:
                 out.append(TensorSpec(self.entry_gate_name + sfx, (self.out_dim, H)))
-            return out + [TensorSpec(self.n["out"] + sfx, (H, self.out_dim))]
+            out.append(TensorSpec(self.n["out"] + sfx, (H, self.out_dim)))
+            if self.bias:
+                sizes = {"q": self.q_dim, "k": self.kv_dim, "v": self.num_kv_heads * self.value_dim, "out": H}
+                out += [TensorSpec(self.n[x] + self.bias_suffix, (sizes[x],), "vector", "bias")
+                        for x in (("q", "out") if self.borrows_keys else ("q", "k", "v", "out"))]
+            if self.carry_blend_name:
+                out.append(TensorSpec(self.carry_blend_name, (), "vector", "bias"))
+            return out
         out = [TensorSpec(self.n["q"] + sfx, (self.q_dim, H)), TensorSpec(self.n["k"] + sfx, (self.kv_dim, H))]
         if self.values == "projected":
             out.append(TensorSpec(self.n["v"] + sfx, (self.kv_dim, H)))
@@ -147,6 +169,14 @@ class AttentionMixer(Part):
                 at += m.shape[0] + pad
             self.w_qkv = torch.cat(rows).contiguous()
             self.w_out = runtime.matrix(read(self.n["out"] + sfx))
+            if self.bias:       # the fused product's bias: every part's own at the part's columns, zero at the gate's and the fill
+                self.b_qkv = torch.zeros(self.w_qkv.shape[0], dtype=torch.float32, device=runtime.device)
+                for x in parts:
+                    b = runtime.vector(read(self.n[x] + self.bias_suffix))
+                    self.b_qkv[self.col[x]:self.col[x] + b.shape[0]] = b
+                self.b_out = runtime.vector(read(self.n["out"] + self.bias_suffix))
+            if self.carry_blend_name:
+                self.carry_blend = runtime.vector(read(self.carry_blend_name)).reshape(1)
             self.position.bind(read, runtime)
             if self.value_rotation:
                 vd = self.value_dim
@@ -185,14 +215,24 @@ class AttentionMixer(Part):
         R, dt, dev = x.shape[0], x.dtype, x.device
         Hq, Hk, D, VD = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
         status = self.runtime.status
-        qkv = linear(self.runtime, x, self.w_qkv)
+        qkv = linear(self.runtime, x, self.w_qkv, self.b_qkv)
         q = torch.empty(R, Hq, D, dtype=dt, device=dev)
         table = step.block_tables[cache.group]
         inv_freq, rot = self.position.fused_rotary()
         own = writes_cache and not self.borrows_keys
+        v_other = None
+        if self.carry_key is not None:
+            # the step's first layer with this key leaves its values for the later ones, which blend theirs with them
+            mine = qkv[:, self.col["v"]:self.col["v"] + Hk * VD]
+            v_other = step.carried.get(self.carry_key) if self.carry_blend is not None else None
+            if self.carry_blend is None:
+                step.carried[self.carry_key] = mine
+            elif v_other is None:
+                raise RuntimeError(f"{self.prefix}: values to blend with under {self.carry_key!r}, and no earlier layer left any")
         ops.qkv_rotate_store(qkv, self.col["q"], self.col["k"] if own else -1, self.col["v"] if own else -1, inv_freq, rot,
                              self.inv_freq_v, step.positions, step.req_of_row, table, cache.page_size, q,
-                             cache.k if own else None, cache.v if own else None, Hq, Hk, D, VD, status)
+                             cache.k if own else None, cache.v if own else None, Hq, Hk, D, VD, status,
+                             float(getattr(self.position, "magnitude", 1.0)), v_other, self.carry_blend)
         gate = qkv[:, self.col["gate"]:] if self.entry_gate_name else None
         fast = self.runtime.attention_kernels
         if fast is not None and hasattr(fast, "attention_flex") and fast.attention_flex(self, q, cache, table, step, gate,
@@ -206,7 +246,7 @@ class AttentionMixer(Part):
         if self.flex:
             o = torch.empty(x.shape[0], self.out_dim, dtype=x.dtype, device=x.device)
             self.forward_inner(x, step, cache, writes_cache, o)
-            return linear(self.runtime, o, self.w_out, out_dtype=torch.float32, defer=True)
+            return linear(self.runtime, o, self.w_out, self.b_out, out_dtype=torch.float32, defer=True)
         R, dt, dev = x.shape[0], x.dtype, x.device
         Hq, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
         status = self.runtime.status

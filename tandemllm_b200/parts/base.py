@@ -167,6 +167,7 @@ class StepContext:
     max_context: int = 0
     host: dict = field(default_factory=dict)   # host-side copies of the lists above (for parts written in torch)
     trace: dict | None = None       # when a dict: parts may record what they decided in this step (eager steps only)
+    carried: dict = field(default_factory=dict)   # device tensors a layer leaves for later layers of the same step, by name
 
 
 class Part:

@@ -14,12 +14,22 @@ A residual add is fused with the norm that follows it, so a layer receives the p
 The norm behind a branch, the residual add and the norm in front of the next sublayer are one kernel where the next
 sublayer is in the same layer (`add_normed(..., then=next norm)`); a layer hands nothing pending to the next one, so
 that whatever a run order adds to the stream between two layers meets a complete residual.
+
+`hyper_connections` carries several residual streams x_1 .. x_S [S, rows, hidden] instead of one. Sublayer q of a layer
+(1: mixer, 2: feed-forward) has three small tensors, `<prefix>hc<q>.in` [S], `.out` [S] and `.mix` [S, S] (indexed [from, to]):
+
+    u = sum_s in[s] x_s;  y = sublayer(norm(u));  x_t <- sum_s mix[s, t] x_s + out[t] y   (all streams at once from the old ones)
+
+What a sublayer leaves is not added by itself here either: it goes on as an `ops.StreamUpdate` (y with its `mix` and `out`),
+and the norm kernel of the next sublayer rewrites the streams, forms the next u with its own `in` and norms it, all in one
+pass over the row. The model starts every stream from the embedded row and sums the streams in front of its last norm.
 """
 
 from __future__ import annotations
 
 from ..config.spec import LayerSpec, PartSpec
 from ..kernels import ops
+from ..weights.loader import TensorSpec
 from .base import ARRANGEMENTS, make_part, register_part
 
 
@@ -56,6 +66,62 @@ class SandwichNormResidual:
         return None
 
 
+class _Reading:
+    """A norm seen by a feed-forward that runs it itself: whatever the feed-forward asks of it, the streams are read with the
+    sublayer's own weights."""
+
+    def __init__(self, norm, read):
+        self.norm, self.read = norm, read
+
+    def add_norm(self, residual, delta, **kw):
+        return self.norm.add_norm(residual, delta.reading(self.read), **kw)
+
+
+@register_part("arrangement", "hyper_connections")
+class HyperConnections:
+    """See the module's text. `params`: `streams` and `names` (in, out, mix: the tensors' names behind `<prefix>hc<q>.`)."""
+    graph_safe = True
+
+    def __init__(self, params=None, prefix: str = ""):
+        params = params or {}
+        self.streams = int(params["streams"])
+        if not 1 <= self.streams <= 8:
+            raise ValueError(f"{self.streams} residual streams: 1 to 8 are implemented")
+        names = params.get("names") or {"in": "in", "out": "out", "mix": "mix"}
+        self.n = {(q, k): f"{prefix}hc{q}.{v}" for q in (1, 2) for k, v in names.items()}
+        self.has_second = bool(params.get("feed_forward", True))
+        self.w = {}
+
+    def weight_specs(self, present=None):
+        S, out = self.streams, []
+        for q in (1, 2) if self.has_second else (1,):
+            out += [TensorSpec(self.n[q, "in"], (S,), "vector", "ones"), TensorSpec(self.n[q, "out"], (S,), "vector", "ones"),
+                    TensorSpec(self.n[q, "mix"], (S, S), "vector", "mix")]
+        return out
+
+    def bind(self, read, runtime):
+        self.w = {key: runtime.vector(read(name)) for key, name in self.n.items() if self.has_second or key[0] == 1}
+
+    def step_bytes(self, elem: int, **_) -> int:
+        return sum(4 * t.numel() for t in self.w.values())
+
+    def run(self, layer: "Layer", residual, pending, step, cache, writes_cache: bool = True):
+        w = self.w
+        if pending is None:
+            pending = ops.StreamUpdate(None, None, None)
+        n = layer.mixer_norm.add_norm(residual, pending.reading(w[1, "in"]))
+        d = ops.StreamUpdate(layer.mixer.forward(n, step, cache, writes_cache=writes_cache), w[1, "mix"], w[1, "out"])
+        ff = layer.feed_forward
+        if getattr(ff, "absent", False):
+            return d
+        norm = _Reading(layer.feed_forward_norm, w[2, "in"])
+        if hasattr(ff, "forward_from"):
+            out = ff.forward_from(norm, residual, d, step)
+        else:
+            out = ff.forward(norm.add_norm(residual, d), step)
+        return ops.StreamUpdate(out, w[2, "mix"], w[2, "out"])
+
+
 class Layer:
     """One layer's parts, built from its spec. The layer knows its parts; no part knows the layer."""
 
@@ -75,12 +141,16 @@ class Layer:
         self.feed_forward = make_part("feed_forward", spec.feed_forward, prefix=p, hidden_size=hidden_size)
         if spec.arrangement not in ARRANGEMENTS:
             raise ValueError(f"unknown arrangement {spec.arrangement!r}; registered: {', '.join(sorted(ARRANGEMENTS))}")
-        self.arrangement = ARRANGEMENTS[spec.arrangement]()
+        cls = ARRANGEMENTS[spec.arrangement]
+        self.arrangement = cls(spec.arrangement_params, prefix=p) if spec.arrangement_params is not None else cls()
 
     @property
     def parts(self):
+        """The layer's parts that have tensors and a say in whether a step may be captured (an arrangement with tensors of its
+        own is one of them)."""
+        own = (self.arrangement,) if hasattr(self.arrangement, "weight_specs") else ()
         return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.feed_forward_norm,
-                                 self.feed_forward, self.feed_forward_post_norm) if p is not None)
+                                 self.feed_forward, self.feed_forward_post_norm) if p is not None) + own
 
     def weight_specs(self, present=None):
         out = []

@@ -217,7 +217,7 @@ class SigmoidTopKExperts(Part):
     def forward_from(self, norm, residual, delta, step):
         """The norm in front and this layer in one go. The router's logits are 32-bit end to end: for few rows the norm
         kernel runs the router itself on its unrounded output as it goes; for many, it also hands the unrounded rows."""
-        route = self.router_args(residual.shape[0], residual.device)
+        route = self.router_args(residual.shape[-2], residual.device)
         if route is not None:
             x = norm.add_norm(residual, delta, route=route)
             return self.forward(x, step, routing=(route["ids"], route["wts"]))
@@ -329,7 +329,7 @@ class SharedAndRouted(Part):
         return self.routed.router_args(rows, device)
 
     def forward_from(self, norm, residual, delta, step):
-        route = self.routed.router_args(residual.shape[0], residual.device)
+        route = self.routed.router_args(residual.shape[-2], residual.device)
         x = norm.add_norm(residual, delta, route=route)
         return self.forward(x, step, routing=(route["ids"], route["wts"]))
 

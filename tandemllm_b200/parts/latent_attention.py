@@ -4,6 +4,9 @@
   [c | k_r] = dkv n;  c = norm(c) * w_dkv (the latent, `kv_rank` numbers);  k_r: one rotated key part for all heads
   head h: key = [uk_h c | rot(k_r)], value = uv_h c;  score = (q_unrotated . uk_h c + rot(q_rotated) . rot(k_r)) * scale
   softmax over the visible keys (0 <= i - j < window, or all); out = o(concatenated heads)
+  with a `sink` tensor named ([heads]): a head's softmax denominator also holds exp(sink_h), which has no key and no value, is
+  not scaled and counts once; with a `gate` matrix named ([heads * value_dim, hidden]): the concatenated heads are multiplied
+  entry by entry by sigmoid(gate n), n the mixer's input, before the out projection
 
 The position encoding is a part of its own (a kind with `fused_rotary_pairs()`); it turns the rotated parts only. What is
 stored a token is c and rot(k_r): one row of kv_rank + rot_dim numbers (`PagedNeed(1, kv_rank + rot_dim, window,
@@ -42,10 +45,15 @@ class LatentAttentionMixer(Part):
             raise ValueError(f"a latent of {self.kv_rank} numbers: up to 512 are implemented")
         self.position = make_part("position_encoding", spec["position"], head_dim=self.rot_dim)
         self.n = {k: prefix + v for k, v in spec["names"].items()}
+        self.has_sink, self.has_gate = "sink" in self.n, "gate" in self.n
+        self.sinks = None
 
     def weight_specs(self, present=None):
         n, W, H = self.n, self.hidden_size, self.heads
-        return [TensorSpec(n["dq"], (self.q_rank, W)), TensorSpec(n["dq_norm"], (self.q_rank,), "vector", "ones"),
+        more = [TensorSpec(n["sink"], (H,), "vector", "bias")] if self.has_sink else []
+        if self.has_gate:
+            more.append(TensorSpec(n["gate"], (H * self.vdim, W)))
+        return more + [TensorSpec(n["dq"], (self.q_rank, W)), TensorSpec(n["dq_norm"], (self.q_rank,), "vector", "ones"),
                 TensorSpec(n["uq"], (H * (self.dim + self.rot_dim), self.q_rank)),
                 TensorSpec(n["dkv"], (self.kv_rank + self.rot_dim, W)),
                 TensorSpec(n["dkv_norm"], (self.kv_rank,), "vector", "ones"),
@@ -55,12 +63,19 @@ class LatentAttentionMixer(Part):
     def bind(self, read, runtime):
         self.runtime = runtime
         n, H = self.n, self.heads
-        # the two down-projections read the same rows: one product, the query's latent first; padded with zero rows so
-        # that the second part begins at a multiple of 8 columns
+        # the two down-projections (and an output gate) read the same rows: one product, the query's latent first; padded
+        # with zero rows so that every part begins at a multiple of 8 columns
         dq, dkv = runtime.matrix(read(n["dq"])), runtime.matrix(read(n["dkv"]))
         self.kv_at = -(-self.q_rank // 8) * 8
         pad = torch.zeros(self.kv_at - self.q_rank, dq.shape[1], dtype=dq.dtype, device=dq.device)
-        self.w_down = torch.cat([dq, pad, dkv]).contiguous()
+        parts = [dq, pad, dkv]
+        if self.has_gate:
+            self.gate_at = self.kv_at + -(-dkv.shape[0] // 8) * 8
+            parts += [torch.zeros(self.gate_at - self.kv_at - dkv.shape[0], dq.shape[1], dtype=dq.dtype, device=dq.device),
+                      runtime.matrix(read(n["gate"]))]
+        self.w_down = torch.cat(parts).contiguous()
+        if self.has_sink:
+            self.sinks = runtime.vector(read(n["sink"]))
         self.w_dq_norm = runtime.vector(read(n["dq_norm"]))
         self.w_dkv_norm = runtime.vector(read(n["dkv_norm"]))
         self.w_uq = runtime.matrix(read(n["uq"]))
@@ -84,7 +99,8 @@ class LatentAttentionMixer(Part):
         cq = torch.empty(R, self.q_rank, dtype=dt, device=dev)
         ops.rmsnorm_rows(down, self.q_rank, self.w_dq_norm, self.eps, cq)
         q = linear(rt, cq, self.w_uq)                           # [R, H (D + Rr)]
-        kv = down[:, self.kv_at:]
+        kv = down[:, self.kv_at:self.kv_at + Dk]
+        gate = down[:, self.gate_at:] if self.has_gate else None
         table = step.block_tables[cache.group]
         inv_freq, rot_dims = self.position.fused_rotary_pairs()
         qa = torch.empty(R, H, Dk, dtype=torch.float32, device=dev)
@@ -94,10 +110,10 @@ class LatentAttentionMixer(Part):
         if D > 0 and (fast is None or not fast.head_linear(q, q.stride(0), D + Rr, self.w_uk_t, qa, H * Dk, Dk, R)):
             ops.head_linear(q, q.stride(0), D + Rr, self.w_uk_t, qa, H * Dk, Dk, R)
         ol = torch.empty(R, H, L, dtype=dt, device=dev)
-        if fast is None or not fast.attention_latent(qa, cache, table, step, self.scale, self.window, ol, L, rt):
+        if fast is None or not fast.attention_latent(qa, cache, table, step, self.scale, self.window, ol, L, rt, self.sinks):
             ops.attention_latent(qa, cache.k, table, cache.page_size, step.req_of_row, step.positions, self.scale, self.window,
-                                 ol, L, rt.status)
+                                 ol, L, rt.status, self.sinks)
         o = torch.empty(R, H * self.vdim, dtype=dt, device=dev)
-        if fast is None or not fast.head_linear(ol, H * L, L, self.w_uv, o, H * self.vdim, self.vdim, R):
-            ops.head_linear(ol, H * L, L, self.w_uv, o, H * self.vdim, self.vdim, R)
+        if fast is None or not fast.head_linear(ol, H * L, L, self.w_uv, o, H * self.vdim, self.vdim, R, gate):
+            ops.head_linear(ol, H * L, L, self.w_uv, o, H * self.vdim, self.vdim, R, gate)
         return linear(rt, o, self.w_out, out_dtype=torch.float32, defer=True)

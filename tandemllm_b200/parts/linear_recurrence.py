@@ -10,6 +10,11 @@ mixer that runs several mixers side by side on the same rows.
     u = k / sqrt(sum k^2 + key_eps) a head: S <- diag(d) S - (a * u)(u^T S) + k v^T, both terms reading the old S; o = S^T r;
     every head's o is brought to unit root mean square on its own, times `norm`, times sigmoid(W_g n), and projected by W_o.
 
+`gated_linear_attention`: q = W_q n * head_dim^(-1/2), k = W_k n (heads x head_dim), v = W_v n (heads x value_dim). A decay a key
+    channel and token, alpha = sigmoid(z)^(1 / tau) with z = W_a2 (W_a1 n) + b (two small products through an inner size that the
+    stored `a1` says): S <- diag(alpha) S + k v^T, o = S^T q with the new S; every head's o is brought to unit root mean square
+    on its own, times the weight `norm` (one head's size, shared by the heads), times silu(W_g n), and projected by W_o.
+
 `weighted_sum`: out = sum_i weight_i mixer_i(n). Each mixer keeps what it needs (pages, a slot) for itself; the weights ride
     in the kernels that form the mixers' concatenated heads, and the out projections are one product over all of them.
 
@@ -161,6 +166,78 @@ class DeltaRuleMixer(Part):
                             max_rows=step.max_rows_per_request)
         return ops.group_norm_gate(y, proj[:, self.col["gate"]:], proj.stride(0), self.w_norm, self.eps, self.heads, out_scale,
                                    out)
+
+    def forward(self, x, step, cache, writes_cache: bool = True):
+        o = torch.empty(x.shape[0], self.out_dim, dtype=x.dtype, device=x.device)
+        self.forward_inner(x, step, cache, writes_cache, o)
+        return linear(self.runtime, o, self.w_out, out_dtype=torch.float32, defer=True)
+
+
+@register_part("mixer", "gated_linear_attention")
+class GatedLinearAttention(Part):
+    graph_safe = True
+
+    def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
+        super().__init__(spec, prefix, hidden_size)
+        self.heads, self.head_dim = int(spec["heads"]), int(spec["head_dim"])
+        self.value_dim = int(spec.get("value_dim") or self.head_dim)
+        if not 1 <= self.head_dim <= 512:
+            raise ValueError(f"a state of {self.head_dim} keys a head: 1 to 512 are implemented")
+        self.eps = float(spec["eps"])
+        self.tau = float(spec["tau"])
+        if not self.tau > 0.0:
+            raise ValueError(f"a decay's root tau = {self.tau}: a positive number")
+        self.n = {k: prefix + v for k, v in spec["names"].items()}
+        self.rank = None        # the inner size of the decay's two products: the shape of `a1` says it
+
+    @property
+    def out_dim(self) -> int:
+        return self.heads * self.value_dim
+
+    def weight_specs(self, present=None):
+        n, W, H, D, VD = self.n, self.hidden_size, self.heads, self.head_dim, self.value_dim
+        rank = self.rank if self.rank is not None else max(8, H * D // 16)
+        return [TensorSpec(n["q"], (H * D, W)), TensorSpec(n["k"], (H * D, W)), TensorSpec(n["v"], (H * VD, W)),
+                TensorSpec(n["gate"], (H * VD, W)), TensorSpec(n["norm"], (VD,), "vector", "ones"),
+                TensorSpec(n["a1"], (rank, W)), TensorSpec(n["a2"], (H * D, rank)),
+                TensorSpec(n["a_bias"], (H * D,), "vector", "bias"), TensorSpec(n["out"], (W, H * VD))]
+
+    def shapes_from(self, shape_of) -> None:
+        shape = shape_of(self.n["a1"])
+        if shape is not None:
+            self.rank = int(shape[0])
+
+    def bind(self, read, runtime):
+        self.runtime = runtime
+        n = self.n
+        # q, k, v and the gate read the same rows: one product whose result stays 32-bit
+        self.w_in, self.col = _stack([(x, runtime.matrix(read(n[x]))) for x in ("q", "k", "v", "gate")])
+        a1, a2 = runtime.matrix(read(n["a1"])), runtime.matrix(read(n["a2"]))
+        # the inner size is filled up with zero rows and columns to a multiple of 8 (16-byte rows for the products)
+        pad = -a1.shape[0] % 8
+        if pad:
+            a1 = torch.cat([a1, torch.zeros(pad, a1.shape[1], dtype=a1.dtype, device=a1.device)]).contiguous()
+            a2 = torch.cat([a2, torch.zeros(a2.shape[0], pad, dtype=a2.dtype, device=a2.device)], dim=1).contiguous()
+        self.w_a1, self.w_a2 = a1, a2
+        self.a_bias = runtime.vector(read(n["a_bias"]))
+        self.w_norm = runtime.vector(read(n["norm"]))
+        self.w_out = runtime.matrix(read(n["out"]))
+
+    def cache_need(self):
+        return SlotNeed((self.heads, self.head_dim, self.value_dim), torch.float32)
+
+    def forward_inner(self, x, step, cache, writes_cache: bool, out: torch.Tensor, out_scale: float = 1.0) -> torch.Tensor:
+        R, dev = x.shape[0], x.device
+        proj = linear(self.runtime, x, self.w_in, out_dtype=torch.float32)
+        # the decay's logits: the inner rows in the compute dtype as the second product's operand, the result 32-bit
+        z = linear(self.runtime, linear(self.runtime, x, self.w_a1), self.w_a2, out_dtype=torch.float32)
+        y = torch.empty(R, self.out_dim, dtype=torch.float32, device=dev)
+        ops.recurrence_scan(proj, self.col["q"], self.col["k"], self.col["v"], cache.state, step.state_slot, step.row_start,
+                            step.n_requests, y, self.heads, self.head_dim, self.value_dim, w=z, w0=self.a_bias,
+                            rate=1.0 / self.tau, write_state=writes_cache, max_rows=step.max_rows_per_request,
+                            q_scale=self.head_dim ** -0.5)
+        return ops.group_norm_gate(y, proj[:, self.col["gate"]:], proj.stride(0), self.w_norm, self.eps, self.heads, out_scale,
+                                   out, gate_activation="silu")
 
     def forward(self, x, step, cache, writes_cache: bool = True):
         o = torch.empty(x.shape[0], self.out_dim, dtype=x.dtype, device=x.device)

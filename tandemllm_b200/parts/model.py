@@ -2,7 +2,9 @@
 
   h = embed[tokens] (times the spec's embedding scale); for each site of the schedule: run its layer on its cache; h = final_norm(h);
   logits = h @ head^T in 32-bit, head = the embedding when tied   (engine/models/lfm2_moe/ref.py:218-241)
-  with a soft cap c in the spec: logits <- c tanh(logits / c)
+  with a soft cap c in the spec: logits <- c tanh(logits / c); with a logit scale: logits <- logits * scale
+  with `streams` in the spec the residual is [streams, rows, hidden], every stream starts as the embedded row, the layers'
+  arrangement rewrites them, and the last norm reads their sum
 
 The model owns no cache: `cache_needs()` tells the cache manager what every site needs and `forward` is
 given the per-site caches it made. It computes the final norm and the head for the wanted rows only.
@@ -124,7 +126,8 @@ class DecoderModel:
     # ---- the forward pass of one batch ----
     def forward(self, step: StepContext, site_caches: list) -> torch.Tensor:
         rt = self.runtime
-        residual = torch.empty(step.n_rows, self.hidden_size, dtype=torch.float32, device=rt.device)
+        shape = (step.n_rows, self.hidden_size)
+        residual = torch.empty((self.spec.streams,) + shape if self.spec.streams else shape, dtype=torch.float32, device=rt.device)
         ops.embed_rows(self.embedding, step.token_ids, residual, rt.status, self.spec.embedding_scale)
         pending = None
         ranges = SETTINGS.is_set("NVTX")             # named ranges for profilers: the step, and each layer in run order
@@ -148,8 +151,12 @@ class DecoderModel:
                 return torch.empty(0, self.vocab_size, dtype=torch.float32, device=rt.device)
             if ranges:
                 torch.cuda.nvtx.range_push("final norm + head")
+            if self.spec.streams:       # the last sublayer's output goes into the streams, whose plain sum is normed
+                pending = (pending or ops.StreamUpdate(None, None, None)).reading(None)
             n = self.final_norm.add_norm(residual, pending, gather=step.out_rows, n_out=step.n_out)
             out = linear(rt, n, self.head, out_dtype=torch.float32)
+            if self.spec.logit_scale != 1.0:
+                ops.activation(out, out, ops.ACTIVATIONS["scale"], float(self.spec.logit_scale))
             if self.spec.logit_softcap:
                 ops.softcap(out, float(self.spec.logit_softcap))
             if ranges:

@@ -2,6 +2,12 @@
 
   y = x * rsqrt(mean(x^2) + eps);  out = w * y      plain w, not 1 + w  (engine/models/lfm2_moe/ref.py:105-109)
 
+A design whose norm weights are stored as their distance from a number (out = (offset + w) * y) names it as `offset` in
+the norm's spec; the sum is formed once at bind time, in 32-bit.
+
+Over a residual of several streams the norm takes an `ops.StreamUpdate` as what is added (see `parts/block.py`,
+`hyper_connections`): the same kernel rewrites the streams and norms their weighed sum.
+
 The residual stream is 32-bit; mean, rsqrt and the scale are 32-bit and the result is rounded once to the
 compute dtype. The reference fuses the same pair (`add_rms`, engine/models/lfm2_moe/kernels.py:90-107).
 """
@@ -24,14 +30,17 @@ class RMSNorm(Part):
         self.size = size
         self.eps = float(spec["eps"])
         self.name = prefix + str(spec.get("tensor") or "weight")     # `tensor`: the weight's own name behind the prefix
+        self.offset = float(spec.get("offset") or 0.0)               # the stored weight is the distance from this number
         self.weight = None
 
     def weight_specs(self, present=None):
-        return [TensorSpec(self.name, (self.size,), role="vector", init="ones")]
+        return [TensorSpec(self.name, (self.size,), role="vector", init="bias" if self.offset else "ones")]
 
     def bind(self, read, runtime):
         self.runtime = runtime
         self.weight = runtime.vector(read(self.name))
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
 
     def add_norm(self, residual: torch.Tensor, delta, out: torch.Tensor | None = None,
                  gather: torch.Tensor | None = None, n_out: int | None = None, want32: bool = False,
@@ -39,7 +48,7 @@ class RMSNorm(Part):
         """residual += delta (32-bit; a tensor or a branch output in one of the deferred forms of `kernels.ops`);
         returns the normed rows in the compute dtype, and with `want32` the pair (normed, the same rows unrounded
         in 32-bit). `route` (see `ops.add_rmsnorm`) also runs a router on the unrounded rows in the same kernel."""
-        rows = residual.shape[0] if gather is None else (n_out if n_out is not None else gather.shape[0])
+        rows = residual.shape[-2] if gather is None else (n_out if n_out is not None else gather.shape[0])
         if out is None:
             out = torch.empty(rows, self.size, dtype=self.runtime.dtype, device=residual.device)
         if not want32:

@@ -10,6 +10,12 @@ l = 2 pi / f, f stays where l < original / high, becomes f / factor where l > or
 (1 - s) f / factor + s f with s = (original / l - low) / (high - low). With `precise` (or a scaling) the frequencies are
 formed in 64-bit and rounded once.
 
+With `scaling` = {factor, original, fast, slow} (`fast` in the place of `low`) the stretch is a ramp over the pairs instead:
+d(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta) is the pair that makes t turns over `original` positions; with
+lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+pair i turns at f_i (1 - ramp_i) + f_i / factor ramp_i, and the sines and cosines are multiplied by `magnitude` =
+0.1 ln(factor) + 1, which the mixer hands to its q/k kernel.
+
 `rope_pairs`: the interleaved layout: entries 2i and 2i + 1 of the rotated part are a pair, (u, v) at position p becomes
 (u cos a - v sin a, v cos a + u sin a) with a = p * theta^(-2i/d), for the first d = `rotary_dim` entries (the rest pass).
 The frequencies are formed once in 64-bit and rounded to 32-bit; angles, sines and cosines are 32-bit in the kernel. A
@@ -30,6 +36,10 @@ import torch
 from .base import Part, register_part
 
 
+RAMP_MAGNITUDE_SLOPE = 0.1      # a ramped stretch multiplies sines and cosines by 1 + slope * ln(factor)
+RAMP_MIN_WIDTH = 0.001
+
+
 @register_part("position_encoding", "rope_neox")
 class RotaryNeox(Part):
     graph_safe = True
@@ -43,13 +53,26 @@ class RotaryNeox(Part):
         self.scaling = spec.get("scaling")
         self.precise = bool(spec.get("precise", False)) or self.scaling is not None
         self.inv_freq = None
+        self.ramped = bool(self.scaling) and "fast" in self.scaling
+        self.magnitude = RAMP_MAGNITUDE_SLOPE * math.log(float(self.scaling["factor"])) + 1.0 if self.ramped else 1.0
 
     def frequencies(self) -> torch.Tensor:
         d = self.rotary_dim
         if not self.precise:
             return 1.0 / (self.theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
         f = self.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)
-        if self.scaling:
+        if self.ramped:
+            s = self.scaling
+            factor, orig = float(s["factor"]), float(s["original"])
+
+            def pair_of(turns: float) -> float:
+                return d * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(pair_of(float(s["fast"]))), 0)
+            hi = min(math.ceil(pair_of(float(s["slow"]))), d - 1)
+            ramp = ((torch.arange(d // 2, dtype=torch.float64) - lo) / max(hi - lo, RAMP_MIN_WIDTH)).clamp(0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+        elif self.scaling:
             s = self.scaling
             factor, low, high, orig = (float(s[k]) for k in ("factor", "low", "high", "original"))
             wavelength = 2.0 * math.pi / f
