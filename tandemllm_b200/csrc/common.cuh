@@ -157,6 +157,7 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 #define TL_ACT_CLAMPED_SWISH 6   // a gate form of its own: g' = min(g, a0), u' = clamp(u, -a0, a0); g' sigmoid(a1 g') (u' + 1)
 #define TL_ACT_SOFTCAP 7     // a0 tanh(z / a0): a soft cap on scores or logits (an activation only, never a gate)
 #define TL_ACT_TANH 8        // tanh(z) (an activation only, never a gate)
+#define TL_ACT_GATE_LAST 8   // the last code a gated product's launcher takes
 #define TL_ACT_SCALE 9       // a0 z (an activation only, never a gate)
 #define TL_ACT_LAST 9
 

@@ -461,8 +461,8 @@ extern "C" int tl_gemm_skinny_grouped(const void* x, long long ldx, const int* r
                              : (tile_group && tile_row0 && tile_rows && n_tiles)),
              "skinny grouped product: operands must be 16-byte aligned and the plan complete, or at most %d pairs given",
              SKINNY_WARPS * 32);
-  TL_REQUIRE(swiglu >= 0 && swiglu <= TL_ACT_LAST, "skinny grouped product: gate activation %d is not one of 0..%d", swiglu,
-             TL_ACT_LAST);
+  TL_REQUIRE(swiglu >= 0 && swiglu <= TL_ACT_GATE_LAST, "skinny grouped product: gate activation %d is not one of 0..%d", swiglu,
+             TL_ACT_GATE_LAST);
   const dim3 grid(ceil_div(N, 16), max_tiles), block(SKINNY_WARPS * 32);
 #define TL_GROUPED(SW_, T_)                                                                                              \
   return (int)launch_chained(gemm_skinny_grouped_kernel<SW_, T_>, grid, block, 0, stream, (const bf16*)x, ldx, row_index,  \

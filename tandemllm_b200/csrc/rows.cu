@@ -702,7 +702,7 @@ p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = exp
 extern "C" int tl_gated_mul(const void* gate_up, void* out, int rows, int inter, int act, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   TL_REQUIRE(rows > 0 && inter > 0, "gated_mul: rows %d width %d", rows, inter);
-  TL_REQUIRE(act >= TL_ACT_SILU && act <= TL_ACT_LAST, "gated_mul: gate activation %d is not one of 1..%d", act, TL_ACT_LAST);
+  TL_REQUIRE(act >= TL_ACT_SILU && act <= TL_ACT_GATE_LAST, "gated_mul: gate activation %d is not one of 1..%d", act, TL_ACT_GATE_LAST);
   const long long n = (long long)rows * inter;
   const long long most = (long long)sm_count() * 16;
   const int blocks = (int)(ceil_div64(n, 256) < most ? ceil_div64(n, 256) : most);

@@ -688,7 +688,7 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   TL_REQUIRE(splits >= 1 && (splits == 1 || (swap && !swiglu && partial && (!tile_group || !reduce))),
              "tensor-core gemm: split-K needs the swapped plain kernel and a workspace (grouped: the caller adds the sums)");
   TL_REQUIRE(!bias || !swiglu, "tensor-core gemm: a bias with the gated epilogue is not implemented");
-  TL_REQUIRE(swiglu >= 0 && swiglu <= TL_ACT_LAST, "tensor-core gemm: gate activation %d is not one of 0..%d", swiglu, TL_ACT_LAST);
+  TL_REQUIRE(swiglu >= 0 && swiglu <= TL_ACT_GATE_LAST, "tensor-core gemm: gate activation %d is not one of 0..%d", swiglu, TL_ACT_GATE_LAST);
   TL_REQUIRE(!row_index || (swap && tile_group && row_div >= 1),
              "tensor-core gemm: a row index needs the swapped grouped kernel (divisor %d)", row_div);
   CUtensorMap tmW, tmX;

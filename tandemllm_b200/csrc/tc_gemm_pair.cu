@@ -533,7 +533,7 @@ static int pair_product(const void* X, long long ldx, long long x_rows, const vo
   TL_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "pair product: operands must be 16-byte aligned (%d)", 0);
   TL_REQUIRE(out_dtype == TL_BF16 || out_dtype == TL_FP32, "pair product: output dtype %d", out_dtype);
   TL_REQUIRE(!bias || !gated, "pair product: a bias with the gated epilogue is not implemented (%d)", gated);
-  TL_REQUIRE(gated >= 0 && gated <= TL_ACT_LAST, "pair product: gate activation %d is not one of 0..%d", gated, TL_ACT_LAST);
+  TL_REQUIRE(gated >= 0 && gated <= TL_ACT_GATE_LAST, "pair product: gate activation %d is not one of 0..%d", gated, TL_ACT_GATE_LAST);
   TL_REQUIRE(!tile_group || (tile_row0 && tile_rows && n_tiles && max_tiles > 0 && plan_rows > 0),
              "pair product: incomplete tile map (tiles of %d rows)", plan_rows);
   TL_REQUIRE(per_sm == 1 || per_sm == 2, "pair product: %d CTAs an SM; 1 or 2", per_sm);

@@ -13,8 +13,8 @@ import math
 
 import numpy as np
 
-YARN_MAGNITUDE_SLOPE = 0.1        # cosines and sines of a stretched rotation are multiplied by 1 + slope * ln(factor)
-YARN_MIN_RAMP_WIDTH = 0.001
+RAMP_MAGNITUDE_SLOPE = 0.1        # cosines and sines of a stretched rotation are multiplied by 1 + slope * ln(factor)
+RAMP_MIN_WIDTH = 0.001
 
 
 def sigmoid(x):
@@ -61,9 +61,9 @@ def stretched_frequencies(base: float, dims: int, scaling: dict | None) -> tuple
     hi = min(math.ceil(d(float(scaling["slow"]))), dims - 1)
     out = f.copy()
     for i in range(dims // 2):
-        ramp = min(max((i - lo) / max(hi - lo, YARN_MIN_RAMP_WIDTH), 0.0), 1.0)
+        ramp = min(max((i - lo) / max(hi - lo, RAMP_MIN_WIDTH), 0.0), 1.0)
         out[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp)
-    return out, YARN_MAGNITUDE_SLOPE * math.log(factor) + 1.0
+    return out, RAMP_MAGNITUDE_SLOPE * math.log(factor) + 1.0
 
 
 def rotate_halves(x: np.ndarray, positions: np.ndarray, freqs: np.ndarray, magnitude: float = 1.0) -> np.ndarray:
@@ -246,5 +246,5 @@ def forward(config: dict, weights: dict, tokens, return_layers: bool = False):
         if streams is not None:
             x = streams.sum(0)
         layers.append(x.copy())
-    logits = offset_norm(x, w["final.norm"], eps) @ w["embed"].T * float(config["logit_scale"])
+    logits = offset_norm(x, w["final.norm"], eps) @ w["embed"].T * float(config.get("logit_scale", 1.0))
     return (logits, np.stack(layers)) if return_layers else logits
