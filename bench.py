@@ -21,6 +21,7 @@ requests at a context of 8192 tokens. A "step" is one decode step of the whole b
 `--design puripel` does the same for Puripel beside an LFM2 MoE model of short-convolution and attention layers.
 `--design sebilorn` does the same for Sebilorn beside an LFM2 model of short-convolution and attention layers with dense
 feed-forwards.
+`--design niralix` does the same for Niralix beside an LFM2 MoE model of short-convolution and attention layers.
 `--design sifupel` measures the Sifupel design beside the closest existing model (an LFM2 configuration of attention layers
 and dense feed-forwards only) at a few equal layer sizes: prefill and decode throughput, and every launch summed by kernel
 family with its fraction of the measured peak (its own line; the default workload and line are untouched).
@@ -357,7 +358,9 @@ class LaunchTimer:
         if name == "tl_gemm_skinny_grouped":
             return "experts gate/up + SwiGLU (register-only)" if args[11] else "experts down (register-only)"
         return {"tl_gemm_skinny_mma": "dense products (register-only)", "tl_gemm_skinny_conv": "in-projection + short conv",
-                "tl_add_rmsnorm": "residual add + norm (+ router, + deferred sums)", "tl_paged_attention_mma": "attention", "tl_paged_attention_tc": "attention",
+                "tl_add_rmsnorm": "residual add + norm (+ router, + deferred sums)",
+                "tl_add_rmsnorm_streams": "residual add + norm (+ router, + deferred sums)", "tl_embed_rows_copies": "embedding",
+                "tl_paged_attention_mma": "attention", "tl_paged_attention_tc": "attention",
                 "tl_paged_attention_split": "attention", "tl_paged_attention_simt": "attention",
                 "tl_attention_join": "attention join", "tl_qk_prepare": "q/k norm + rotary + cache write",
                 "tl_moe_plan": "routing plan", "tl_gather_rows": "rows into expert order", "tl_short_conv": "short conv",
@@ -925,6 +928,174 @@ def sebilorn_compare(a) -> int:
     return 0
 
 
+NIRALIX_SIZES = {
+    "1k": dict(width=1024, layers=8, vocab=32768, streams=2, heads=16, kv=4, dim=64, vdim=64, rot=64, ff=2816, experts=16, top=4,
+               expert_ff=704, gla_heads=16, gla_dim=64, gla_vdim=64, lat_heads=16, lat_dim=64, lat_rot=32, lat_vdim=64,
+               kv_rank=256, q_rank=384, context=1024),
+    "2k": dict(width=2048, layers=12, vocab=65536, streams=4, heads=16, kv=4, dim=128, vdim=128, rot=64, ff=5632, experts=32,
+               top=4, expert_ff=1408, gla_heads=16, gla_dim=128, gla_vdim=128, lat_heads=16, lat_dim=128, lat_rot=64,
+               lat_vdim=128, kv_rank=512, q_rank=768, context=2048),
+}
+
+
+def niralix_compare(a) -> int:
+    """Niralix beside the closest existing model at equal width, depth, vocabulary, heads and feed-forward sizes: an LFM2 MoE
+    model of short-convolution and attention layers (attention where Niralix attends, over keys and values or over a latent; a
+    short convolution where Niralix carries a matrix state; dense SwiGLU where Niralix is dense, routed experts where it
+    routes). Niralix's layers repeat: gated linear attention + dense, attention with carried values + experts, latent
+    attention + dense, gated linear attention + experts; its residual is `streams` streams. Random weights. For each: a
+    prompt of `--prefill-tokens` tokens, decode steps of `--batch` requests at the sizes' context (device-timed, from CUDA
+    graphs where the engine takes them), and one eager decode step and one prefill with every launch timed and summed by
+    kernel family. Work: attention 2 (dim + vdim) flops a visible (row, key, head), latent attention 2 (2 kv_rank + rot_dim),
+    and, decoding, the bytes of the visible cached rows; the recurrence 6 32-bit flops a (row, head, key, value) on the
+    CUDA cores and, decoding, the states read and written; the norms the 32-bit rows they read and write (every stream in and
+    out, the sublayer's output in, the normed row out)."""
+    import torch
+
+    from tandemllm_b200.config import Lfm2MoeConfig, NiralixConfig
+    from tandemllm_b200.engine import Engine, EngineArgs, StepEntry
+    from tandemllm_b200.kernels import ops
+    from tandemllm_b200.sampling import SamplingParams
+    pk = peaks()
+    tokens, batch = a.prefill_tokens, a.batch
+    elem = 2 if a.dtype == "bfloat16" else 4
+    out = []
+    for label in (a.design_sizes.split(",") if a.design_sizes else NIRALIX_SIZES):
+        z = NIRALIX_SIZES[label]
+        W, L, V, S, H, G, D, VD = (z[k] for k in ("width", "layers", "vocab", "streams", "heads", "kv", "dim", "vdim"))
+        context = z["context"]
+        dense = {"kind": "dense", "ff": z["ff"]}
+        moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["expert_ff"]}}
+        att = {"heads": H, "kv_heads": G, "dim": D, "vdim": VD, "scale": D ** -0.5, "v_mix": True,
+               "rot": {"base": 500000.0, "dims": z["rot"], "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+        gla = {"heads": z["gla_heads"], "dim": z["gla_dim"], "vdim": z["gla_vdim"], "tau": 16.0}
+        lat = {"heads": z["lat_heads"], "dim": z["lat_dim"], "rot_dim": z["lat_rot"], "vdim": z["lat_vdim"],
+               "kv_rank": z["kv_rank"], "q_rank": z["q_rank"], "scale": (z["lat_dim"] + z["lat_rot"]) ** -0.5,
+               "rot": {"base": 10000.0, "dims": z["lat_rot"]}}
+        cycle = [("gla", gla, dense), ("attention", att, moe), ("latent_attention", lat, dense), ("gla", gla, moe)]
+        layers = [{"type": cycle[i % 4][0], "mixer": dict(cycle[i % 4][1]), "mlp": cycle[i % 4][2]} for i in range(L)]
+        nir = NiralixConfig.from_dict({"architecture": "Niralix", "vocab": V, "width": W, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+                                       "streams": S, "layers": layers})
+        routed = [i for i in range(L) if i % 4 in (1, 3)]
+        lfm = Lfm2MoeConfig.from_dict(dict(
+            CONFIG_8B, vocab_size=V, hidden_size=W, intermediate_size=z["ff"], moe_intermediate_size=z["expert_ff"],
+            num_experts=z["experts"], num_experts_per_tok=z["top"], num_hidden_layers=L, num_attention_heads=H,
+            num_key_value_heads=G, head_dim=D, num_dense_layers=L - len(routed),      # (its dense layers come first)
+            layer_types=["conv" if i % 4 in (0, 3) else "full_attention" for i in range(L)]))
+        n_gla, n_att, n_lat = (sum(1 for i in range(L) if i % 4 in ks) for ks in ((0, 3), (1,), (2,)))
+        row = {"sizes": dict(z, label=label), "prefill_tokens": tokens, "batch": batch, "context": context}
+        for name, cfg in (("niralix", nir), ("lfm2_moe_conv_attention", lfm)):
+            room = max(context, tokens) + 4 * a.steps + 64
+            engine = Engine.from_config(cfg, seed=0, args=EngineArgs(
+                dtype=a.dtype, max_len=room, parallel=batch, block_size=16, max_batched_tokens=max(tokens, batch),
+                chunk_size=tokens, graph=a.graph == "on"))
+            for sc in engine.cache.site_cache:
+                for c in (sc if isinstance(sc, tuple) else (sc,)):
+                    if hasattr(c, "k") and c.k is not None:
+                        c.k.normal_(0, 0.5)
+                        if c.v is not None and c.v is not c.k:
+                            c.v.normal_(0, 0.5)
+            g = torch.Generator().manual_seed(1)
+            fn = engine.step_function
+
+            def prefill_once():
+                engine.admit("prefill")
+                prompt = torch.randint(0, V, (tokens,), generator=g).tolist()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                engine.step([StepEntry("prefill", prompt, [tokens - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                engine.release("prefill")
+                return e0.elapsed_time(e1)
+            prefill_once()
+            pre_ms = statistics.median(prefill_once() for _ in range(3))
+            timer = LaunchTimer()
+            with timer:
+                prefill_once()
+                pre_table = timer.table()
+            greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
+            reqs = [start_with_context(engine, torch.randint(0, V, (context,), generator=g).tolist(),
+                                       SamplingParams(**vars(greedy))) for _ in range(batch)]
+            fn.check_status = False
+            toks = torch.randint(0, V, (3 * a.steps + a.warmup + 4, batch), generator=g).tolist()
+            picked = torch.empty(batch, dtype=torch.int32, device=engine.device)
+
+            def one(i):
+                ops.argmax(fn.run([StepEntry(r.request_id, [toks[i][j]], [0]) for j, r in enumerate(reqs)]), picked)
+            for i in range(a.warmup):
+                one(i)
+            torch.cuda.synchronize()
+            regions = []
+            for rep in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(a.warmup + rep * a.steps, a.warmup + (rep + 1) * a.steps):
+                    one(i)
+                e1.record()
+                torch.cuda.synchronize()
+                regions.append(e0.elapsed_time(e1) / a.steps)
+            dec_ms = statistics.median(regions)
+            kept, fn.use_graphs = fn.use_graphs, False
+            one(3 * a.steps + a.warmup)
+            with timer:
+                one(3 * a.steps + a.warmup + 1)
+                dec_table = timer.table()
+            fn.use_graphs = kept
+            fn.check_status = True
+            fn.raise_on_fault()
+            for t in (pre_table, dec_table):
+                for r in t.values():
+                    r["ms"] = round(r["ms"], 4)
+            entry = {"prefill": {"ms": round(pre_ms, 3), "tok_s": round(tokens / pre_ms * 1e3, 1), "families": pre_table},
+                     "decode": {"ms_per_step": round(dec_ms, 4), "tok_s": round(batch / dec_ms * 1e3, 1),
+                                "graphs": bool(engine.model.graph_safe and a.graph == "on"),
+                                "weight_bytes_per_step": engine.model.decode_bytes(batch)["total"], "families": dec_table}}
+            entry["decode"]["frac_hbm_weights_only"] = round(entry["decode"]["weight_bytes_per_step"] / dec_ms / 1e6 / pk["hbm_gbs"], 4)
+            pairs = tokens * (tokens + 1) // 2
+            norms = 2 * L + 1
+            if name == "niralix":
+                work = {"attention": (2.0 * (D + VD) * H * pairs * n_att, float(elem) * batch * G * (D + VD) * context * n_att),
+                        "latent attention": (2.0 * (2 * z["kv_rank"] + z["lat_rot"]) * z["lat_heads"] * pairs * n_lat,
+                                             float(elem) * batch * (z["kv_rank"] + z["lat_rot"]) * context * n_lat),
+                        "matrix-state recurrence": (6.0 * tokens * z["gla_heads"] * z["gla_dim"] * z["gla_vdim"] * n_gla,
+                                                    8.0 * batch * z["gla_heads"] * z["gla_dim"] * z["gla_vdim"] * n_gla)}
+                norm_row = W * (4.0 * (2 * S + 1) + elem)
+            else:
+                n_full = sum(1 for i in range(L) if i % 4 in (1, 2))
+                work = {"attention": (4.0 * D * H * pairs * n_full, float(elem) * batch * G * 2 * D * context * n_full)}
+                norm_row = W * (4.0 * 3 + elem)
+            fam_norm = "residual add + norm (+ router, + deferred sums)"
+            for table, rows_ in ((pre_table, tokens), (dec_table, batch)):
+                if fam_norm in table:
+                    rate = norm_row * rows_ * norms / table[fam_norm]["ms"] / 1e6
+                    table[fam_norm]["GBps_rows_only"] = round(rate, 1)
+                    table[fam_norm]["frac_hbm_rows_only"] = round(rate / pk["hbm_gbs"], 4)
+            for fam, (flops, nbytes) in work.items():
+                if fam in pre_table and flops:
+                    rate = flops / pre_table[fam]["ms"] / 1e9
+                    pre_table[fam]["TFLOPs"] = round(rate, 2)
+                    if a.dtype == "bfloat16" and fam != "matrix-state recurrence":
+                        pre_table[fam]["frac_of_measured_bf16"] = round(rate / pk["bf16_tflops"], 4)
+                if fam in dec_table and nbytes:
+                    rate = nbytes / dec_table[fam]["ms"] / 1e6
+                    dec_table[fam]["GBps"] = round(rate, 1)
+                    dec_table[fam]["frac_hbm"] = round(rate / pk["hbm_gbs"], 4)
+            row[name] = entry
+            for r in reqs:
+                r.num_computed = engine.cache.length_of(r.request_id)
+                engine.scheduler.abort(r)
+            del engine, fn, reqs
+            torch.cuda.empty_cache()
+        out.append(row)
+    print(json.dumps({"design_compare": "niralix beside lfm2 moe (short convolution and attention layers, dense and routed feed-forwards)",
+                      "dtype": a.dtype, "peaks": pk,
+                      "data": "synthetic: random weights, uniform random token ids, random cached rows as context",
+                      "rows": out}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -959,16 +1130,16 @@ def main() -> int:
                     help="programmatic dependent launch between the kernels (for comparison; ordinary launches by default)")
     ap.add_argument("--profile", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--design", choices=("sifupel", "puripel", "sebilorn"),
+    ap.add_argument("--design", choices=("sifupel", "puripel", "sebilorn", "niralix"),
                     help="measure this design beside the closest existing model at equal layer sizes (its own line)")
     ap.add_argument("--design-sizes", default="", help="--design: which of " + ", ".join(DESIGN_SIZES) + " (sifupel) or "
-                    + ", ".join(PURIPEL_SIZES) + " (puripel) or " + ", ".join(SEBILORN_SIZES) + " (sebilorn) (default: all)")
+                    + ", ".join(PURIPEL_SIZES) + " (puripel) or " + ", ".join(SEBILORN_SIZES) + " (sebilorn) or " + ", ".join(NIRALIX_SIZES) + " (niralix) (default: all)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
     if a.design:
         a.warmup = max(a.warmup, 3)
-        return {"puripel": puripel_compare, "sebilorn": sebilorn_compare}.get(a.design, design_compare)(a)
+        return {"puripel": puripel_compare, "sebilorn": sebilorn_compare, "niralix": niralix_compare}.get(a.design, design_compare)(a)
     if a.gpus != 1:
         print(json.dumps({"error": f"this engine runs on one GPU; --gpus {a.gpus} is not implemented", "n_gpus": a.gpus}))
         return 2

@@ -207,6 +207,8 @@ class NiralixConfig:
                 else:
                     position = PartSpec("none", {})
                 carry = None
+                if not m.get("v_mix"):
+                    ignored.append(f"l{i}.mix.vmix")      # a blend weight stored for a layer that does not blend: never read
                 if m.get("v_mix"):
                     # the first such layer's own blend weight is stored and never used
                     carry = {"key": CARRY_KEY, "blend": "mix.vmix" if first_mix is not None else None}
@@ -232,6 +234,8 @@ class NiralixConfig:
             mlp = layer.mlp
             if mlp is None:
                 ff = PartSpec("none", {})
+                # what a folder may still hold for the sublayer that is not there
+                ignored += [f"l{i}.norm2"] + [f"l{i}.hc2.{x}" for x in ("in", "out", "mix")]
             elif mlp["kind"] == "dense":
                 ff = PartSpec("swiglu", {"intermediate_size": int(mlp["ff"]), "activation": "silu", "weight_suffix": "",
                                          "names": {"gate": "mlp.gate", "up": "mlp.up", "down": "mlp.down"}})

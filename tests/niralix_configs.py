@@ -192,7 +192,7 @@ def random_config(seed: int) -> tuple[dict, int]:
     and feed-forwards. Returns (config, the decay's inner size)."""
     import random
     r = random.Random(seed)
-    W = r.choice([24, 40, 64, 72])
+    W = r.choice([24, 36, 40, 50, 64, 72, 100])
     mixing = None          # (kv heads, vdim) that every value-mixing layer shares
     layers = []
     for _ in range(r.randint(2, 5)):

@@ -296,7 +296,7 @@ def test_experts_chosen_by_softmax_scores_keep_their_scores(dtype, E, k, ff, row
     # a row whose k-th and (k+1)-th scores nearly tie may choose otherwise: such rows are left out
     srt = np.sort(scores, axis=-1)[:, ::-1]
     clear = (srt[:, k - 1] - srt[:, k] > 1e-5 * srt[:, 0]) if k < E else np.ones(rows, bool)
-    assert clear.sum() >= max(1, rows - 2)
+    assert clear.sum() >= max(1, int(0.9 * rows))
     assert rel(out[torch.from_numpy(clear)], want[clear]) < TOL[dtype] * (3 if dtype == "bfloat16" else 1)
 
 

@@ -30,8 +30,9 @@ def test_the_reader_names_every_tensor_of_the_design():
                 if hasattr(part, "shapes_from"):
                     part.shapes_from(lambda n: shapes.get(n))
         got = {s.name: tuple(s.shape) for s in model.weight_specs(None)}
-        # the first value-mixing layer's own blend weight is stored and never read
-        assert set(shapes) - set(got) == set(spec.ignored_names), name
+        # the first value-mixing layer's own blend weight is stored and never read (the other ignored names are what a folder
+        # may hold for a sublayer or a blend that is not there)
+        assert set(shapes) - set(got) <= set(spec.ignored_names) and not set(got) & set(spec.ignored_names), name
         assert got == {k: v for k, v in shapes.items() if k not in spec.ignored_names}, name
         assert NiralixConfig.from_dict(NiralixConfig.from_dict(cfg).to_dict()).to_spec() == spec
 
@@ -51,7 +52,7 @@ def test_caches_states_and_streams_follow_the_configuration():
     # the first mixing layer leaves its values, the later ones blend with them
     carries = [l.mixer.get("value_carry") for l in spec.layers]
     assert carries[1]["blend"] is None and carries[3]["blend"] == "mix.vmix" and carries[1]["key"] == carries[3]["key"]
-    assert spec.ignored_names == ("l1.mix.vmix",)
+    assert "l1.mix.vmix" in spec.ignored_names and "l3.mix.vmix" not in spec.ignored_names
     plain = NiralixConfig.from_dict(C.N3).to_spec()
     assert plain.streams == 0 and all(l.arrangement == "prenorm_residual" for l in plain.layers)
     assert all(l.mixer.get("value_carry") is None for l in plain.layers if l.mixer.kind == "attention")
