@@ -283,8 +283,9 @@ __device__ __forceinline__ void router_logits_one_row(const NormParams& p, const
 // the unrounded row in 32-bit, and the choice and weights are written as well.
 // ROUTE_PER: 0 without a router (a small kernel, three blocks an SM), else the experts a lane of the choosing warp holds.
 // ONE_ROW: the launch gives every block one row (a decode step: few blocks, which may take all the registers they like).
-template <typename T, int ROUTE_PER, bool ONE_ROW>
-__global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) add_rmsnorm_kernel(NormParams p) {
+// STREAMS: the residual is several streams (see NormParams); a kernel of its own, so that the plain one stays as lean as it was.
+template <typename T, int ROUTE_PER, bool ONE_ROW, bool STREAMS>
+__global__ void __launch_bounds__(512, (ONE_ROW || STREAMS) ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) add_rmsnorm_kernel(NormParams p) {
   // rows_per_block rows of `hidden` floats, 33 for the reduction, then rows_per_block x E logits
   extern __shared__ __align__(16) float rows_buf[];
   float* scratch = rows_buf + (size_t)p.rows_per_block * p.hidden;
@@ -340,7 +341,7 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
     __syncthreads();
   }
   float* res = p.residual + (size_t)r * hidden;
-  const bool hyper = p.streams > 0;              // several streams: what is added rewrites them, and their weighed sum is normed
+  constexpr bool hyper = STREAMS;               // several streams: what is added rewrites them, and their weighed sum is normed
   const bool adds = !hyper && (p.delta || p.expert_rows);
   const bool hyper_writes = hyper && !p.gather && rank == 0;
   const bool vec = (hidden & 3) == 0;           // rows are then 16-byte aligned: four elements a step
@@ -428,7 +429,7 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
           }
           x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
         }
-        if (hyper) x = hyper_streams<float4>(p, (size_t)r, c, x, hyper_writes);
+        if constexpr (hyper) x = hyper_streams<float4>(p, (size_t)r, c, x, hyper_writes);
         reinterpret_cast<float4*>(row)[c] = x;
         ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
       }
@@ -450,7 +451,7 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
           }
           x += d;
         }
-        if (hyper) x = hyper_streams<float>(p, (size_t)r, c, x, hyper_writes);
+        if constexpr (hyper) x = hyper_streams<float>(p, (size_t)r, c, x, hyper_writes);
         row[c] = x;
         ss += x * x;
       }
@@ -672,12 +673,18 @@ p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = exp
     p.split = out_rows <= ROUTER_SPLIT_ROWS ? ROUTER_SPLIT : (out_rows <= 37 ? 4 : (out_rows <= 74 ? 2 : 1));
   const dim3 grid(ceil_div(out_rows, rows_per_block) * p.split);
   const int per = !router_w ? 0 : (E <= 32 ? 1 : (E <= 128 ? 4 : MAX_EXPERTS / 32));
-#define TL_NORM1(T_, PER_, ONE_)                                                                                          \
+#define TL_NORM2(T_, PER_, ONE_, STREAMS_)                                                                                \
   do {                                                                                                                    \
     if (smem > 48 * 1024)                                                                                                 \
-      cudaFuncSetAttribute(add_rmsnorm_kernel<T_, PER_, ONE_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
-    if (p.split > 1) return (int)launch_clustered(add_rmsnorm_kernel<T_, PER_, ONE_>, grid, dim3(threads), smem, stream, p.split, p); \
-    return (int)launch_chained(add_rmsnorm_kernel<T_, PER_, ONE_>, grid, dim3(threads), smem, stream, p);                 \
+      cudaFuncSetAttribute(add_rmsnorm_kernel<T_, PER_, ONE_, STREAMS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (p.split > 1)                                                                                                      \
+      return (int)launch_clustered(add_rmsnorm_kernel<T_, PER_, ONE_, STREAMS_>, grid, dim3(threads), smem, stream, p.split, p); \
+    return (int)launch_chained(add_rmsnorm_kernel<T_, PER_, ONE_, STREAMS_>, grid, dim3(threads), smem, stream, p);       \
+  } while (0)
+#define TL_NORM1(T_, PER_, ONE_)                    \
+  do {                                              \
+    if (streams > 0) TL_NORM2(T_, PER_, ONE_, true); \
+    TL_NORM2(T_, PER_, ONE_, false);                \
   } while (0)
 #define TL_NORM(T_, PER_)                          \
   do {                                             \
@@ -696,6 +703,7 @@ p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = exp
   TL_NORM(bf16, MAX_EXPERTS / 32);
 #undef TL_NORM
 #undef TL_NORM1
+#undef TL_NORM2
 }
 
 // out [rows, inter] = act(gate_up[:, :inter]) * gate_up[:, inter:], act one of TL_ACT_SILU .. TL_ACT_IDENTITY
