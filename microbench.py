@@ -141,11 +141,19 @@ def attention(a) -> dict:
 def norm(a) -> dict:
     from tandemllm_b200.kernels import ops
     ops.core()
-    R, H = a.rows, a.hidden
-    res = torch.randn(R, H, device=DEV)
+    R, H, S = a.rows, a.hidden, a.streams
     delta = torch.randn(R, H, device=DEV)
     w = torch.ones(H, device=DEV)
     out = torch.empty(R, H, dtype=torch.bfloat16, device=DEV)
+    if S:       # several residual streams: rewritten from the old ones and the sublayer's output, their weighed sum normed
+        res = torch.randn(S, R, H, device=DEV)
+        mix = (torch.eye(S) * 0.9 + 0.1 / S).to(DEV)
+        upd = ops.StreamUpdate(delta, mix, torch.ones(S, device=DEV), torch.full((S,), 1.0 / S, device=DEV))
+        ms = timed(lambda: ops.add_rmsnorm(res, upd, w, 1e-5, out), a.iters)
+        nbytes = R * H * (4 * (2 * S + 1) + 2)
+        return {"kernel": "streams rewritten + RMS norm", "rows": R, "hidden": H, "streams": S, "ms": ms, "bytes": nbytes,
+                "GBps": nbytes / ms / 1e6}
+    res = torch.randn(R, H, device=DEV)
     ms = timed(lambda: ops.add_rmsnorm(res, delta, w, 1e-5, out), a.iters)
     nbytes = R * H * (4 + 4 + 4 + 2)
     return {"kernel": "residual add + RMS norm", "rows": R, "hidden": H, "ms": ms, "bytes": nbytes, "GBps": nbytes / ms / 1e6}
@@ -241,7 +249,7 @@ def latent(a) -> dict:
 
 
 def recurrence(a) -> dict:
-    """The recurrence over a matrix state a head of one layer (`--rule delta` or `decay`): `batch` requests of `rows` rows."""
+    """The recurrence over a matrix state a head of one layer (`--rule delta`, `decay` or `gated`): `batch` requests of `rows` rows."""
     from tandemllm_b200.kernels import ops
     ops.core()
     H, D, VD, B, R = a.heads, a.dim, a.vdim, a.batch, a.rows
@@ -257,6 +265,8 @@ def recurrence(a) -> dict:
     start = torch.arange(0, (B + 1) * R, R, dtype=torch.int32, device=DEV)
     kw = dict(a_col=cols["a"], w=torch.randn(B * R, I, device=DEV), w0=torch.zeros(I, device=DEV), a_bias=torch.zeros(I, device=DEV),
               rate=0.6, key_eps=1e-6) if delta else dict(head_decay=torch.full((H,), 0.97, device=DEV), silu_inputs=True)
+    if a.rule == "gated":       # a decay a key channel and token, sigmoid(w + w0)^rate
+        kw = dict(w=torch.randn(B * R, I, device=DEV), w0=torch.full((I,), 3.0, device=DEV), rate=1.0 / 16, q_scale=D ** -0.5)
     ms = timed(lambda: ops.recurrence_scan(proj, cols["q"], cols["k"], cols["v"], state, slot, start, B, y, H, D, VD,
                                            max_rows=R, **kw), a.iters)
     flops = (10.0 if delta else 6.0) * B * R * H * D * VD
@@ -350,7 +360,7 @@ def main(argv=None) -> int:
     la.add_argument("--kv-rank", type=int, default=256)
     la.add_argument("--rot-dim", type=int, default=32)
     rc = sub.add_parser("recurrence")
-    rc.add_argument("--rule", default="delta", choices=("delta", "decay"))
+    rc.add_argument("--rule", default="delta", choices=("delta", "decay", "gated"))
     rc.add_argument("--batch", type=int, default=1)
     rc.add_argument("--rows", type=int, default=2048)
     rc.add_argument("--heads", type=int, default=16)
@@ -371,6 +381,7 @@ def main(argv=None) -> int:
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=8)
     n.add_argument("--hidden", type=int, default=2048)
+    n.add_argument("--streams", type=int, default=0, help="several residual streams (hyper-connections); 0: one residual")
     for p in (e, d):
         p.add_argument("--product", default="pair", choices=("pair", "single"),
                        help="prompt-sized products: the kernel on pairs of SMs (cta_group::2), or the one-CTA persistent kernel")

@@ -89,20 +89,25 @@ struct NormParams {
 
 constexpr int MAX_STREAMS = 8;
 
-// One 16-byte piece (or, with N = 1, one number) of a row across all streams: rewrites the streams from y and returns what the
-// norm reads. Every sum runs over the streams in ascending order, the sublayer's output last.
+// One 16-byte piece (or, with V = float, one number) of a row in every stream. Asked for at the top of an iteration, before what
+// is added is put together, so that all of an iteration's loads are in flight at once.
 template <typename V>
-__device__ __forceinline__ V hyper_streams(const NormParams& p, size_t r, int c, V y, bool write) {
-  constexpr int N = sizeof(V) / sizeof(float);
-  const int S = p.streams;
-  float xs[MAX_STREAMS][N];
+struct StreamPieces {
+  V x[MAX_STREAMS];
+};
+template <typename V>
+__device__ __forceinline__ void hyper_load(const NormParams& p, size_t r, int c, StreamPieces<V>& in) {
 #pragma unroll
   for (int s = 0; s < MAX_STREAMS; ++s)
-    if (s < S) {
-      const V v = reinterpret_cast<const V*>(p.residual + (long long)s * p.stream_stride + r * p.hidden)[c];
-#pragma unroll
-      for (int i = 0; i < N; ++i) xs[s][i] = reinterpret_cast<const float*>(&v)[i];
-    }
+    if (s < p.streams) in.x[s] = reinterpret_cast<const V*>(p.residual + (long long)s * p.stream_stride + r * p.hidden)[c];
+}
+
+// Rewrites the streams' pieces from the sublayer's output y and returns what the norm reads. Every sum runs over the streams in
+// ascending order, the sublayer's output last.
+template <typename V>
+__device__ __forceinline__ V hyper_streams(const NormParams& p, size_t r, int c, const StreamPieces<V>& in, V y, bool write) {
+  constexpr int N = sizeof(V) / sizeof(float);
+  const int S = p.streams;
   float u[N];
 #pragma unroll
   for (int i = 0; i < N; ++i) u[i] = 0.f;
@@ -118,7 +123,7 @@ __device__ __forceinline__ V hyper_streams(const NormParams& p, size_t r, int c,
           if (s < S) {
             const float m = p.hc_mix[s * S + t];
 #pragma unroll
-            for (int i = 0; i < N; ++i) nt[i] = fmaf(m, xs[s][i], nt[i]);
+            for (int i = 0; i < N; ++i) nt[i] = fmaf(m, reinterpret_cast<const float*>(&in.x[s])[i], nt[i]);
           }
         const float o = p.hc_out[t];
         V out;
@@ -130,7 +135,7 @@ __device__ __forceinline__ V hyper_streams(const NormParams& p, size_t r, int c,
         if (write) reinterpret_cast<V*>(p.residual + (long long)t * p.stream_stride + r * p.hidden)[c] = out;
       } else {
 #pragma unroll
-        for (int i = 0; i < N; ++i) nt[i] = xs[t][i];
+        for (int i = 0; i < N; ++i) nt[i] = reinterpret_cast<const float*>(&in.x[t])[i];
       }
       const float w = p.hc_in ? p.hc_in[t] : 1.f;
 #pragma unroll
@@ -387,7 +392,10 @@ __global__ void __launch_bounds__(512, (ONE_ROW || STREAMS) ? 1 : (ROUTE_PER <= 
       const int h4 = hidden >> 2;
       const float4* res4 = reinterpret_cast<const float4*>(res);
       for (int c = t; c < h4; c += G) {
-        float4 x = hyper ? make_float4(0.f, 0.f, 0.f, 0.f) : res4[c];       // (several streams: x is first the sublayer's output)
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);       // (several streams: x is first the sublayer's output)
+        StreamPieces<float4> pieces;
+        if constexpr (hyper) hyper_load(p, (size_t)r, c, pieces);
+        else x = res4[c];
         if (p.delta) {
           float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
           for (int s = 0; s < p.parts; ++s) {
@@ -429,13 +437,16 @@ __global__ void __launch_bounds__(512, (ONE_ROW || STREAMS) ? 1 : (ROUTE_PER <= 
           }
           x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
         }
-        if constexpr (hyper) x = hyper_streams<float4>(p, (size_t)r, c, x, hyper_writes);
+        if constexpr (hyper) x = hyper_streams<float4>(p, (size_t)r, c, pieces, x, hyper_writes);
         reinterpret_cast<float4*>(row)[c] = x;
         ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
       }
     } else {
       for (int c = t; c < hidden; c += G) {
-        float x = hyper ? 0.f : res[c];
+        float x = 0.f;
+        StreamPieces<float> pieces;
+        if constexpr (hyper) hyper_load(p, (size_t)r, c, pieces);
+        else x = res[c];
         if (p.delta) {
           float d = 0.f;
           for (int s = 0; s < p.parts; ++s) d += p.delta[(long long)s * p.part_stride + (size_t)r * hidden + c];
@@ -451,7 +462,7 @@ __global__ void __launch_bounds__(512, (ONE_ROW || STREAMS) ? 1 : (ROUTE_PER <= 
           }
           x += d;
         }
-        if constexpr (hyper) x = hyper_streams<float>(p, (size_t)r, c, x, hyper_writes);
+        if constexpr (hyper) x = hyper_streams<float>(p, (size_t)r, c, pieces, x, hyper_writes);
         row[c] = x;
         ss += x * x;
       }
