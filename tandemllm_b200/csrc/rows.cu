@@ -103,29 +103,32 @@ __device__ __forceinline__ void hyper_load(const NormParams& p, size_t r, int c,
 }
 
 // Rewrites the streams' pieces from the sublayer's output y and returns what the norm reads. Every sum runs over the streams in
-// ascending order, the sublayer's output last.
-template <typename V>
-__device__ __forceinline__ V hyper_streams(const NormParams& p, size_t r, int c, const StreamPieces<V>& in, V y, bool write) {
+// ascending order, the sublayer's output last. `hc`: the block's copy of the weights in shared memory, mix [S, S], then out [S],
+// then in [S] (ones where the plain sum is read). NS: the number of streams when the compiler knows it, else 0.
+template <typename V, int NS>
+__device__ __forceinline__ V hyper_streams_n(const NormParams& p, const float* __restrict__ hc, size_t r, int c,
+                                             const StreamPieces<V>& in, V y, bool write) {
   constexpr int N = sizeof(V) / sizeof(float);
-  const int S = p.streams;
+  const int S = NS > 0 ? NS : p.streams;
+  constexpr int TOP = NS > 0 ? NS : MAX_STREAMS;
   float u[N];
 #pragma unroll
   for (int i = 0; i < N; ++i) u[i] = 0.f;
 #pragma unroll
-  for (int t = 0; t < MAX_STREAMS; ++t)
+  for (int t = 0; t < TOP; ++t)
     if (t < S) {
       float nt[N];
       if (p.hc_mix) {
 #pragma unroll
         for (int i = 0; i < N; ++i) nt[i] = 0.f;
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s)
+        for (int s = 0; s < TOP; ++s)
           if (s < S) {
-            const float m = p.hc_mix[s * S + t];
+            const float m = hc[s * S + t];
 #pragma unroll
             for (int i = 0; i < N; ++i) nt[i] = fmaf(m, reinterpret_cast<const float*>(&in.x[s])[i], nt[i]);
           }
-        const float o = p.hc_out[t];
+        const float o = hc[S * S + t];
         V out;
 #pragma unroll
         for (int i = 0; i < N; ++i) {
@@ -137,7 +140,7 @@ __device__ __forceinline__ V hyper_streams(const NormParams& p, size_t r, int c,
 #pragma unroll
         for (int i = 0; i < N; ++i) nt[i] = reinterpret_cast<const float*>(&in.x[t])[i];
       }
-      const float w = p.hc_in ? p.hc_in[t] : 1.f;
+      const float w = hc[S * S + S + t];
 #pragma unroll
       for (int i = 0; i < N; ++i) u[i] = fmaf(w, nt[i], u[i]);
     }
@@ -145,6 +148,17 @@ __device__ __forceinline__ V hyper_streams(const NormParams& p, size_t r, int c,
 #pragma unroll
   for (int i = 0; i < N; ++i) reinterpret_cast<float*>(&ret)[i] = u[i];
   return ret;
+}
+
+template <typename V>
+__device__ __forceinline__ V hyper_streams(const NormParams& p, const float* __restrict__ hc, size_t r, int c,
+                                           const StreamPieces<V>& in, V y, bool write) {
+  switch (p.streams) {          // the counts a model is likely to have, as straight-line code
+    case 1: return hyper_streams_n<V, 1>(p, hc, r, c, in, y, write);
+    case 2: return hyper_streams_n<V, 2>(p, hc, r, c, in, y, write);
+    case 4: return hyper_streams_n<V, 4>(p, hc, r, c, in, y, write);
+    default: return hyper_streams_n<V, 0>(p, hc, r, c, in, y, write);
+  }
 }
 
 // With a router and many rows, a block norms this many rows before it multiplies them by the router's weights,
@@ -349,6 +363,14 @@ __global__ void __launch_bounds__(512, (ONE_ROW || STREAMS) ? 1 : (ROUTE_PER <= 
   constexpr bool hyper = STREAMS;               // several streams: what is added rewrites them, and their weighed sum is normed
   const bool adds = !hyper && (p.delta || p.expert_rows);
   const bool hyper_writes = hyper && !p.gather && rank == 0;
+  __shared__ float s_hc[STREAMS ? MAX_STREAMS * MAX_STREAMS + 2 * MAX_STREAMS : 1];
+  if constexpr (hyper) {
+    const int S = p.streams;
+    for (int i = threadIdx.x; i < S * S + 2 * S; i += blockDim.x)
+      s_hc[i] = i < S * S ? (p.hc_mix ? p.hc_mix[i] : 0.f)
+                          : (i < S * S + S ? (p.hc_out ? p.hc_out[i - S * S] : 0.f) : (p.hc_in ? p.hc_in[i - S * S - S] : 1.f));
+    __syncthreads();
+  }
   const bool vec = (hidden & 3) == 0;           // rows are then 16-byte aligned: four elements a step
   float ss = 0.f;
   // A row that gets a plain tensor added (or nothing) and whose thread holds at most IN_REGS 16-byte pieces of it: all
@@ -437,7 +459,7 @@ __global__ void __launch_bounds__(512, (ONE_ROW || STREAMS) ? 1 : (ROUTE_PER <= 
           }
           x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
         }
-        if constexpr (hyper) x = hyper_streams<float4>(p, (size_t)r, c, pieces, x, hyper_writes);
+        if constexpr (hyper) x = hyper_streams<float4>(p, s_hc, (size_t)r, c, pieces, x, hyper_writes);
         reinterpret_cast<float4*>(row)[c] = x;
         ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
       }
@@ -462,7 +484,7 @@ __global__ void __launch_bounds__(512, (ONE_ROW || STREAMS) ? 1 : (ROUTE_PER <= 
           }
           x += d;
         }
-        if constexpr (hyper) x = hyper_streams<float>(p, (size_t)r, c, pieces, x, hyper_writes);
+        if constexpr (hyper) x = hyper_streams<float>(p, s_hc, (size_t)r, c, pieces, x, hyper_writes);
         row[c] = x;
         ss += x * x;
       }
