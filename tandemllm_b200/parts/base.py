@@ -25,6 +25,10 @@ Interfaces (duck-typed; the base classes below document them and hold the shared
   Arrangement     run(layer, residual, pending, step, cache, writes_cache) -> pending  (the not-yet-added branch output)
                   An arrangement that norms a branch's output too reads `layer.mixer_post_norm` and
                   `layer.feed_forward_post_norm` (norms with `add_normed(residual, delta, ...)`: residual += norm(delta)).
+                  An arrangement with sizes and tensors of its own (`LayerSpec.arrangement_params`) is built with
+                  (params, prefix=) and has `weight_specs(present)`, `bind(read, runtime)` and `graph_safe` like a part;
+                  over a model whose spec names `streams` its `residual` is [streams, rows, hidden] and what it hands on is
+                  an `ops.StreamUpdate`, which the next norm's kernel takes into the streams.
 
 A branch output is what a mixer or feed-forward adds to the residual stream: a float32 tensor [R, hidden], or one of
 the deferred forms of `kernels.ops` (`PartialSums`, `ExpertRows`) that the next norm kernel adds itself;

@@ -143,6 +143,8 @@ class DecoderModel:
                                                f"{type(layer.feed_forward).__name__}")
                 if site.add is not None:
                     # (what is pending is added by the layer's first norm; the order of the two additions is free)
+                    if self.spec.streams:
+                        raise NotImplementedError("a vector added between layers to a residual of several streams")
                     ops.add_vector(residual, self.stream_adds[site.add.tensor][site.add.row])
                 pending = self.layers[site.layer].run(residual, pending, step, cache, writes_cache=own)
                 if ranges:

@@ -496,3 +496,47 @@ def test_models_drawn_at_random(seed, dtype):
     schedule = [[("a", 40), ("b", 1)], [("a", 2), ("b", 17), ("c", 2)], [("a", 1), ("b", 1)], [("a", 31), ("b", 11)],
                 [("a", 23)]]
     held_to_the_plain_model(engine, cfg, W, toks, schedule, dtype, f"random {seed}", slack=2.0 if dtype == "bfloat16" else 1.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_command_line_writes_a_random_model_and_generates_from_it(dtype, tmp_path):
+    """`random-weights` from a config.json of this design (the names the architecture stores, the blend weight that is never
+    read left out), then `generate` on the folder: greedy tokens that the plain model agrees with."""
+    from tandemllm_b200.weights.safetensors_io import index_file, read_tensor
+    cfg_path, folder, out = tmp_path / "config.json", tmp_path / "m", tmp_path / "out.json"
+    cfg_path.write_text(json.dumps(C.N1))
+    base = [sys.executable, "-m", "tandemllm_b200"]
+    r = subprocess.run(base + ["random-weights", "--config", str(cfg_path), "--seed", "5", "--out", str(folder)], cwd=ROOT,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    prompt = C.tokens("n1", 19, seed=6)
+    r = subprocess.run(base + ["generate", "--model", str(folder), "--dtype", dtype, "--prompt-ids", ",".join(map(str, prompt)),
+                               "--tokens", "8", "--json", str(out)], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = json.loads(out.read_text())["outputs"][0]
+    assert len(got) == 8
+    W = {k: read_tensor(v).double().numpy() for k, v in index_file(str(folder / "model.safetensors")).items()}
+    W.setdefault("l1.mix.vmix", np.array(0.0))
+    text = list(prompt)
+    for t in got:
+        row = P.forward(C.N1, W, text)[-1]
+        assert float(row.max() - row[t]) <= (2e-3 if dtype == "float32" else 0.12) * float(np.abs(row).max())
+        text.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_model_of_real_layer_widths(dtype):
+    """Layer sizes of a model that would be served (width 1024, heads of 64 and 128, a latent of 256, 16 experts, 4 streams),
+    few layers and a small vocabulary: the products, attentions and scans run the forms they take at such sizes (prompt-sized
+    tensor-core products, tiles of 64 rows, staged scans). A prompt in two portions, then decoding beside a second request."""
+    cfg = {"architecture": "Niralix", "vocab": 1000, "width": 1024, "norm": {"eps": 1e-6}, "logit_scale": 0.5, "streams": 4,
+           "layers": [C._gla(16, 64, 64, 16.0, ff=(16, 4, 256)),
+                      C._attn(16, 4, 64, 64, 0.125, C._rot(500000.0, 64, (8.0, 8192, 32.0, 1.0)), v_mix=True, ff=1024),
+                      C._latent(16, 64, 32, 64, 256, 384, 96 ** -0.5, 10000.0, ff=(16, 4, 256)),
+                      C._attn(8, 4, 128, 64, 0.09, C._rot(500000.0, 32, (8.0, 8192, 32.0, 1.0)), v_mix=True, ff=1024)]}
+    W = C.random_weights(cfg, 16, 77)
+    engine, cfg, W = engine_of(None, dtype, cfg=cfg, W=W, pages=32)
+    g = torch.Generator().manual_seed(9)
+    toks = {r: torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for r, n in (("a", 200), ("b", 70))}
+    schedule = [[("a", 150)], [("a", 40), ("b", 64)]] + [[("a", 1), ("b", 1)]] * 6 + [[("a", 4)]]
+    held_to_the_plain_model(engine, cfg, W, toks, schedule, dtype, "real widths")
