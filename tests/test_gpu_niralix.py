@@ -124,7 +124,7 @@ def test_the_norm_kernel_rewrites_the_streams_and_norms_what_the_sublayer_reads(
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,dim,vdim,tau,rank", [(3, 8, 6, 4.0, 5), (2, 64, 64, 16.0, 16), (3, 40, 72, 8.0, 12), (1, 16, 16, 1.0, 8),
-                                                     (2, 128, 128, 16.0, 8), (5, 1, 3, 2.0, 2), (6, 32, 64, 16.0, 16)])
+                                                     (2, 128, 128, 16.0, 8), (5, 1, 3, 2.0, 2), (5, 32, 96, 32.0, 24)])
 def test_gated_linear_attention_in_portions_in_slots_used_again_and_a_first_token_that_lasts(dtype, heads, dim, vdim, tau, rank):
     """Two requests side by side, one whole and one in portions down to single tokens; a third request takes a slot that was
     given back and must find it zero; with decays near one the first token still shows hundreds of tokens later."""
@@ -192,7 +192,7 @@ ATTN_CASES = {
     # heads, kv, dim, vdim, scale, rot dims, scaling
     "narrow values, half a head turned, a stretch": (4, 2, 16, 8, 0.3, 8, (4.0, 64, 8.0, 2.0)),
     "tensor-core sizes": (8, 2, 64, 64, 0.125, 32, (8.0, 256, 16.0, 1.0)),
-    "one kv head, keys of 128 over values of 32": (4, 1, 128, 32, 0.09, 32, (2.0, 2048, 32.0, 1.0)),
+    "one kv head, keys of 128 over values of 48": (6, 1, 128, 48, 0.09, 64, (3.0, 1024, 16.0, 0.5)),
     "as many kv heads as heads, no stretch": (2, 2, 32, 16, 0.15, 16, None),
     "no rotation": (3, 1, 24, 40, 0.2, 0, None),
     "keys of 128, values of 64": (4, 2, 128, 64, 0.09, 64, None),
@@ -239,7 +239,7 @@ def test_attention_with_biases_a_stretch_and_carried_values_reaches_a_far_key(ca
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,D,R,VD,L,Q", [(3, 12, 4, 10, 20, 14), (4, 64, 32, 64, 64, 48), (1, 8, 16, 24, 16, 8), (4, 64, 16, 64, 128, 96),
+@pytest.mark.parametrize("H,D,R,VD,L,Q", [(3, 12, 4, 10, 20, 14), (4, 64, 32, 64, 64, 48), (1, 8, 16, 24, 16, 8), (6, 48, 16, 64, 128, 72),
                                           (2, 32, 8, 128, 320, 40)])
 def test_latent_attention_with_a_sink_and_an_output_gate(dtype, H, D, R, VD, L, Q):
     """Hundreds of keys, portions across pages' edges, token by token; sinks from far below every score (no effect) to above
@@ -265,7 +265,7 @@ def test_latent_attention_with_a_sink_and_an_output_gate(dtype, H, D, R, VD, L, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("E,k,ff,rows", [(5, 2, 24, 37), (8, 3, 64, 300), (2, 1, 40, 5), (4, 4, 16, 1), (16, 3, 64, 20)])
+@pytest.mark.parametrize("E,k,ff,rows", [(5, 2, 24, 37), (8, 3, 64, 300), (2, 1, 40, 5), (4, 4, 16, 1), (24, 5, 48, 20)])
 def test_experts_chosen_by_softmax_scores_keep_their_scores(dtype, E, k, ff, rows):
     from tandemllm_b200.parts import make_part
     width = 72

@@ -88,7 +88,7 @@ def test_unknown_keys_and_bad_sizes_are_refused_by_name():
 
 def test_the_engines_frequencies_are_the_plain_ones():
     from tandemllm_b200.parts.position import RotaryNeox
-    cases = [(10000.0, 8, None), (500000.0, 32, (2.0, 2048, 32.0, 1.0)), (100.0, 16, (8.0, 64, 8.0, 2.0)),
+    cases = [(10000.0, 8, None), (300000.0, 48, (3.0, 1024, 16.0, 0.5)), (100.0, 16, (8.0, 64, 8.0, 2.0)),
              (50000.0, 128, (2.0, 128, 1e9, 1e-9)), (300.0, 2, (4.0, 16, 3.0, 1.0))]
     for base, dims, scaling in cases:
         s = dict(zip(("factor", "original", "fast", "slow"), scaling)) if scaling else None
